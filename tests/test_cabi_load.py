@@ -44,19 +44,6 @@ def test_version_and_argument_errors_without_gpu(lib):
     assert lib.atx_paged_attn_decode_workspace_bytes(6, 32, 128, 1) == 0
 
 
-def test_sass_uses_blackwell_tensor_and_tma_paths():
-    import shutil
-    import subprocess
-
-    from atx import _cabi
-
-    if shutil.which("cuobjdump") is None:
-        pytest.skip("cuobjdump not on PATH")
-    sass = subprocess.run(["cuobjdump", "-sass", str(_cabi.lib_path())], capture_output=True, text=True).stdout
-    assert "UTCHMMA" in sass and "UTMALDG" in sass and "LDTM" in sass   # tcgen05.mma / TMA / tcgen05.ld
-    assert "sm_100a" in sass
-
-
 def test_tokenizer_stub_roundtrip_and_template():
     from atx.tokenizer import ByteTokenizer, llama3_chat_string
 
