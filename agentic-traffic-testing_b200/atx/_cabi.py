@@ -22,6 +22,8 @@ GEMM_SWIGLU_BF16 = 3
 FLAG_PDL = 1
 FLAG_ORDERED = 2   # atx_gemm_run ADD_F32, T <= 64: fixed-order split-K (bit-reproducible)
 FLAG_ADD_BF16 = 4  # atx_rmsnorm: the `add` buffer is bf16
+DT_BF16 = 0        # element type of weights / GEMM inputs / KV pages in the calls that take one
+DT_F32 = 1
 
 EXPORTS = [
     "atx_last_error", "atx_version", "atx_device_info",
@@ -31,6 +33,8 @@ EXPORTS = [
     "atx_paged_attn_decode_workspace_bytes", "atx_paged_attn_decode", "atx_paged_attn_prefill",
     "atx_paged_attn_decode_static", "atx_paged_attn_decode_static_capacity",
     "atx_sample", "atx_sample_shard", "atx_sample_merge",
+    "atx_gemm_simple", "atx_embed_rows", "atx_concat_embed", "atx_resid_norm", "atx_gated_act", "atx_gated_norm",
+    "atx_conv_dt", "atx_conv_state_update", "atx_linear_recurrence", "atx_qk_prepare", "atx_attn_local",
 ]
 
 
@@ -91,6 +95,21 @@ def load() -> C.CDLL:
     lib.atx_sample.argtypes = [vp, i64, vp, vp, vp, vp, vp, i32, i32, i32, vp]
     lib.atx_sample_shard.argtypes = [vp, i64, i32, vp, vp, vp, vp, i32, i32, i32, vp]
     lib.atx_sample_merge.argtypes = [vp, i32, i32, vp, i32, vp]
+    lib.atx_gemm_simple.argtypes = [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, vp]
+    lib.atx_embed_rows.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.atx_concat_embed.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
+    lib.atx_resid_norm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
+    lib.atx_gated_act.argtypes = [vp, vp, i32, i32, i32, i32, vp]
+    lib.atx_gated_norm.argtypes = [vp, i64, vp, i64, vp, vp, i64, i32, i32, i32, f32, i32, f32, i32, i32, vp]
+    lib.atx_conv_dt.argtypes = [vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
+                                i32, i32, vp]
+    lib.atx_conv_state_update.argtypes = [vp, i64, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
+    lib.atx_linear_recurrence.argtypes = [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp,
+                                          i64, vp, vp, vp, vp, i32, i32, vp]
+    lib.atx_qk_prepare.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32,
+                                   i32, i32, i32, i32, f32, i32, i32, vp]
+    lib.atx_attn_local.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, f32, f32,
+                                   i32, i32, f32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

@@ -35,6 +35,8 @@ class ModelConfig:
     max_position_embeddings: int = 131072
     eos_token_ids: tuple = (128001, 128008, 128009)  # <|end_of_text|>, <|eom_id|>, <|eot_id|>
     bos_token_id: int = 128000
+    architecture = "llama"       # key of the model registry (atx/models)
+    recurrent = False            # no per-sequence state besides the KV pages
 
     @property
     def q_size(self) -> int:
@@ -85,6 +87,17 @@ def model_config_by_name(name: str, num_layers: Optional[int] = None) -> ModelCo
     if num_layers is not None:
         cfg.num_hidden_layers = num_layers
     return cfg
+
+
+def model_config_from_json(path: Path):
+    """config.json -> the configuration class of its model family (the key `architecture`, else HF's `model_type`)."""
+    d = json.loads(Path(path).read_text())
+    arch = d.get("architecture")
+    if arch is not None:
+        from .models import config_class_for
+
+        return config_class_for(arch).from_json(d, name=str(Path(path).parent.name))
+    return model_config_from_hf_json(path)
 
 
 def model_config_from_hf_json(path: Path) -> ModelConfig:
@@ -140,12 +153,17 @@ def resolve_model(model: str) -> ModelSource:
     """
     if model.startswith("random:"):
         parts = model.split(":")
+        from .models import random_shape
+
+        cfg = random_shape(parts[1])
+        if cfg is not None:     # a named shape of another model family
+            return ModelSource(cfg, None, int(parts[2]) if len(parts) > 2 and parts[2] else 0)
         seed = int(parts[2]) if len(parts) > 2 and parts[2] else 0
         layers = int(parts[3]) if len(parts) > 3 and parts[3] else None
         return ModelSource(model_config_by_name(parts[1], layers), None, seed)
     p = Path(model)
     if p.is_dir() and (p / "config.json").exists():
-        return ModelSource(model_config_from_hf_json(p / "config.json"), p, None)
+        return ModelSource(model_config_from_json(p / "config.json"), p, None)
     snap = _hub_snapshot(model)
     if snap is not None:
         return ModelSource(model_config_from_hf_json(snap / "config.json"), snap, None)
@@ -177,6 +195,8 @@ class EngineConfig:
     #                                 every run of the same batches, a few percent slower per decode step
     tp_allreduce: str = "auto"      # tensor parallel: "auto" = our fused all-reduce + add + norm kernels for steps of up
     #                                 to 256 rows (push form up to 64), NCCL beyond; "nccl" = NCCL for every step
+    dtype: str = "bfloat16"         # "float32": weights, GEMMs and caches in true 32-bit (model families that have it)
+    max_logit_rows: Optional[int] = None   # rows of a step whose logits can be asked for (default: max_num_seqs)
     device: int = 0
     tp_size: int = 1          # tensor-parallel ranks sharing one model (70B); needs torch.distributed NCCL
     tp_rank: int = 0

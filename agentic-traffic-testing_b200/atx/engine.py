@@ -16,7 +16,7 @@ from typing import AsyncIterator, Callable, Dict, List, Optional, Sequence as Se
 import torch
 
 from .config import EngineConfig, ModelConfig, ModelSource, resolve_model
-from .kv_cache import BlockAllocator
+from .kv_cache import BlockAllocator, StateSlotPool
 from .runner import ModelRunner
 from .scheduler import SamplingParams, Scheduler, Sequence, SeqState
 from .weights import ModelWeights
@@ -40,16 +40,29 @@ class LLMEngine:
         self.ecfg = ecfg
         dev = torch.device("cuda", ecfg.device)
         torch.cuda.set_device(dev)
+        arch = getattr(self.mcfg, "architecture", "llama")
         if weights is None:
-            if source.path is not None:
+            if arch != "llama":      # other families: the registry's weight container, in the engine's element type
+                from . import models
+
+                xt = torch.float32 if ecfg.dtype == "float32" else torch.bfloat16
+                weights = (models.load_weights(self.mcfg, source.path, dev, xt) if source.path is not None else
+                           models.random_weights(self.mcfg, source.random_seed or 0, dev, xt))
+            elif source.path is not None:
                 weights = ModelWeights.from_hf_dir(self.mcfg, source.path, dev, ecfg.tp_size, ecfg.tp_rank)
             else:
                 weights = ModelWeights.random(self.mcfg, source.random_seed or 0, dev, tp_size=ecfg.tp_size,
                                               tp_rank=ecfg.tp_rank)
         self.runner = ModelRunner(self.mcfg, ecfg, weights)
-        self.allocator = BlockAllocator(self.runner.num_blocks, ecfg.block_size, ecfg.enable_prefix_caching)
+        # a model with recurrent state gives every live sequence a state slot, and a cached prefix cannot be attached
+        # to a new sequence (its pages would be there, the state after it would not)
+        recurrent = bool(getattr(self.mcfg, "recurrent", False))
+        self.state_slots = StateSlotPool(ecfg.max_num_seqs) if recurrent else None
+        self.allocator = BlockAllocator(self.runner.num_blocks, ecfg.block_size,
+                                        ecfg.enable_prefix_caching and not recurrent)
         self.scheduler = Scheduler(self.allocator, ecfg.max_num_seqs, ecfg.max_num_batched_tokens, ecfg.max_model_len,
-                                   self.mcfg.eos_token_ids)
+                                   self.mcfg.eos_token_ids, state_slots=self.state_slots)
+        self._fed: Dict[str, Sequence] = {}   # sequences driven by feed()
         self.steps = 0
         self.batch_size_observer: Optional[Callable[[int], None]] = None
         self._inflight = None   # (plan, launch handle) of a step whose tokens the host has not read yet
@@ -129,6 +142,50 @@ class LLMEngine:
         touched = self.scheduler.commit(plan, sampled)
         self._inflight = nxt
         return touched + plan.finished
+
+    # ---- teacher-forced stepping: the caller dictates the tokens and how they are cut into steps ---------------
+    def feed(self, entries, end=()) -> "np.ndarray":
+        """One engine step over exactly the given portions: `entries` is a list of (request_id, token ids, wanted
+        offsets). A request is admitted at its first portion and continues from its pages and state at every later
+        one; requests listed in `end` give their pages and state slot back after the step. Returns the fp32 logits at
+        the wanted offsets, [n_wanted, vocab], in the order of the entries. Same scheduler structures, runner step
+        and kernels as generation; nothing is sampled into the sequences."""
+        import numpy as np
+
+        if self._inflight is not None:
+            raise RuntimeError("feed() while a generation step is in flight")
+        V = self.mcfg.vocab_size
+        portions = []
+        for rid, toks, want in entries:
+            toks = [int(t) for t in toks]
+            if not toks or any(t < 0 or t >= V for t in toks):
+                raise ValueError(f"{rid}: empty portion or token id outside the vocabulary")
+            if any(k < 0 or k >= len(toks) for k in want):
+                raise ValueError(f"{rid}: wanted offset outside the portion")
+            seq = self._fed.get(rid)
+            if seq is None:
+                seq = self._fed[rid] = Sequence(rid, toks, SamplingParams(temperature=0.0, max_tokens=1, ignore_eos=True),
+                                                self.allocator)
+            else:
+                seq.tokens.extend(toks)
+                seq.prompt_len = len(seq.tokens)
+            if len(seq.tokens) > self.ecfg.max_model_len:
+                raise ValueError(f"{rid}: {len(seq.tokens)} tokens exceed max_model_len={self.ecfg.max_model_len}")
+            portions.append((seq, len(toks), list(want)))
+        plan = self.scheduler.plan_explicit(portions)
+        handle = self.runner.launch(plan)
+        self.runner.wait(handle)
+        n_rows = len(plan.decodes) + sum(len(c.want_rows or []) for c in plan.prefills)
+        logits = self.runner.read_logits(n_rows) if any(w for _, _, w in portions) else np.zeros((0, V), np.float32)
+        self.steps += 1
+        self.scheduler.commit(plan, {})
+        by_seq = {c.seq.uid: c for c in plan.decodes + plan.prefills}
+        idx = [r for seq, _, _ in portions for r in by_seq[seq.uid].want_rows]
+        for rid in end:
+            seq = self._fed.pop(rid, None)
+            if seq is not None:
+                self.scheduler.retire(seq)
+        return logits[idx] if idx else np.zeros((0, V), np.float32)
 
     def generate_sync(self, prompts: List[Seq[int]], params: SamplingParams) -> List[List[int]]:
         """Blocking helper for tests and the bench: run the given prompts to completion."""

@@ -125,6 +125,36 @@ class BlockAllocator:
                 del self._cached[key]
 
 
+class StateSlotPool:
+    """Slots of the fixed-size per-sequence state that recurrent mixers carry (device arrays [num_slots, ...] owned by
+    the model's program). A sequence holds one slot from admission until it finishes or is preempted; a slot is handed
+    out again as it is, because a sequence that starts at position 0 never reads what the slot held before."""
+
+    def __init__(self, num_slots: int):
+        if num_slots <= 0:
+            raise ValueError("num_slots must be positive")
+        self.num_slots = num_slots
+        self._free: Deque[int] = deque(range(num_slots))
+        self._held = [False] * num_slots
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def acquire(self) -> Optional[int]:
+        if not self._free:
+            return None
+        s = self._free.popleft()
+        self._held[s] = True
+        return s
+
+    def release(self, slot: int) -> None:
+        if not self._held[slot]:
+            raise RuntimeError(f"double release of state slot {slot}")
+        self._held[slot] = False
+        self._free.append(slot)
+
+
 class SequenceBlocks:
     """Block table of one sequence plus the hash chain of its full blocks."""
 

@@ -61,7 +61,48 @@ class ModelRunner:
             raise ValueError(f"block_size={self.bs}: KV pages hold 16 tokens (vLLM's default; the prefill attention "
                              "loads one page of one KV head per TMA box)")
         self.MB = (e.max_model_len + self.bs - 1) // self.bs
+        self.arch = getattr(mcfg, "architecture", "llama")
+        if e.dtype not in ("bfloat16", "float32"):
+            raise ValueError(f"dtype={e.dtype!r}: expected bfloat16 | float32")
+        if self.arch == "llama" and e.dtype != "bfloat16":
+            raise ValueError("the Llama path computes in bfloat16 (fp32 residual, norms and softmax); it has no float32 mode")
+        # rows of a step that can have logits: one per sequence (sampling) unless the caller asks for more
+        self.Rmax = max(self.Smax, 16, e.max_logit_rows or 0)
+        self.layer_probe: Optional[list] = None   # debugging: a list that receives the residual after every layer run
+        self.program = None                       # layer program of a non-Llama family (atx/models)
         self.tp, self.tp_rank, self.tp_group = max(1, e.tp_size), e.tp_rank, None
+        self.allreduce_calls = 0
+        self.fused_ar = False      # all-reduce + add + norm in our own kernels over peer memory (else: NCCL + norm kernel)
+        dev = self.dev
+        R = self.Rmax
+        self.logits = torch.zeros(R, mcfg.vocab_size, dtype=torch.float32, device=dev)
+        self.out_ids = torch.zeros(R, dtype=torch.int32, device=dev)
+        self.out_host = [torch.zeros(R, dtype=torch.int32).pin_memory() for _ in range(2)]  # ping-pong: one step may be in flight
+        self._out_events = [torch.cuda.Event(), torch.cuda.Event()]
+        self._out_flip = 0
+        self._init_staging()
+        if self.arch == "llama":
+            self._init_llama()
+        else:
+            from .models import make_program
+
+            self.program = make_program(self)     # allocates its buffers, pages and state pools; sets num_blocks
+        self._graphs: Dict[Tuple[int, int, bool], torch.cuda.CUDAGraph] = {}
+        self._graph_launches: Dict[Tuple[int, int, bool], int] = {}
+        self._graphs_ok = self.program is None or getattr(self.program, "graph_safe", False)
+        self.stream = torch.cuda.Stream(device=dev)   # every launch and copy of this runner
+        self._h2d_done = torch.cuda.Event()
+        self.flags = (_cabi.FLAG_PDL if e.use_pdl else 0) | (_cabi.FLAG_ORDERED if e.deterministic else 0)
+        self.launches_last_step = 0
+        self.kernel_launches = 0  # cumulative count of our kernels launched (graph replays included)
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+        # bench hook: when a list, every step appends (start_event, end_event, n_decode, prefill_tokens, ctx_sum)
+        self.step_events: Optional[list] = None
+
+    def _init_llama(self) -> None:
+        """Buffers, GEMM plans and KV pools of the built-in Llama layer schedule."""
+        m, e, weights = self.m, self.e, self.w
         tp = self.tp
         if tp > 1:
             import torch.distributed as dist
@@ -77,7 +118,7 @@ class ModelRunner:
         qkv_size = m.qkv_size // tp
         bf, f32, i32 = torch.bfloat16, torch.float32, torch.int32
         dev = self.dev
-        T, S = self.Tmax, max(self.Smax, 16)
+        T, S = self.Tmax, self.Rmax
         self.h = torch.zeros(T, H, dtype=f32, device=dev)
         self.qkv = torch.zeros(T, qkv_size, dtype=f32, device=dev)
         self.q = torch.zeros(T, q_size, dtype=bf, device=dev)
@@ -86,8 +127,6 @@ class ModelRunner:
         self.part = torch.zeros(T, H, dtype=f32, device=dev) if tp > 1 else None  # partial o/down sums (TP)
         # ... of prefill-sized steps: stored and all-reduced in bf16 (half the NCCL bytes; what vLLM reduces too)
         self.part_bf = torch.zeros(T, H, dtype=bf, device=dev) if tp > 1 else None
-        self.allreduce_calls = 0
-        self.fused_ar = False      # all-reduce + add + norm in our own kernels over peer memory (else: NCCL + norm kernel)
         self.xn = self.xn2 = self.xl = None
         if e.tp_allreduce not in ("auto", "nccl"):
             raise ValueError(f"tp_allreduce={e.tp_allreduce!r}: expected auto | nccl")
@@ -98,46 +137,13 @@ class ModelRunner:
             self.xl = torch.zeros(S, H, dtype=bf, device=dev)
         if self.xn2 is None:
             self.xn2 = self.xn    # input of gate_up; a buffer of its own only under the low-latency all-reduce
-        self.logits = torch.zeros(S, V, dtype=f32, device=dev)
-        self.out_ids = torch.zeros(S, dtype=i32, device=dev)
         if tp > 1:   # (score, global index) of this rank's vocabulary shard per row, and every rank's after the exchange
             self.pairs = torch.zeros(S, 2, dtype=f32, device=dev)
             self.pairs_all = torch.zeros(tp, S, 2, dtype=f32, device=dev)
-        self.out_host = [torch.zeros(S, dtype=i32).pin_memory() for _ in range(2)]  # ping-pong: one step may be in flight
-        self._out_events = [torch.cuda.Event(), torch.cuda.Event()]
-        self._out_flip = 0
         self.rope = rope_table(m, e.max_model_len, dev)
         self.max_splits = 32
         self.ws = torch.zeros(max(1, _cabi.decode_workspace_bytes(S, m.num_attention_heads // tp, m.head_dim,
                                                                   self.max_splits) // 4), dtype=f32, device=dev)
-
-        # ---- staged integer / float inputs: one pinned host mirror, one device buffer -----------
-        S_ = self.Smax
-        off, self._off = 0, {}
-
-        def region(name: str, n: int) -> None:
-            nonlocal off
-            off = (off + 3) // 4 * 4  # 16-byte aligned regions
-            self._off[name] = (off, n)
-            off += n
-
-        for name, n in (("ids", T), ("pos", T), ("slots", T), ("dec_lens", S_), ("pf_cu", S_ + 1), ("pf_ctx", S_),
-                        ("rows", S_), ("steps", S_), ("temps", S_), ("top_p", S_), ("seeds", 2 * S_),
-                        ("dec_bt", S_ * self.MB), ("pf_bt", S_ * self.MB)):
-            region(name, n)
-        self._meta_lo = self._off["dec_lens"][0]
-        self._meta_hi = self._off["seeds"][0] + self._off["seeds"][1]
-        self.hbuf = torch.zeros(off, dtype=i32).pin_memory()
-        self.dbuf = torch.zeros(off, dtype=i32, device=dev)
-        self.hnp = self.hbuf.numpy()
-        self._hv = {k: self.hnp[o:o + n] for k, (o, n) in self._off.items()}
-        self._hv["temps_f"] = self._hv["temps"].view(np.float32)
-        self._hv["top_p_f"] = self._hv["top_p"].view(np.float32)
-        self._hv["seeds_q"] = self._hv["seeds"].view(np.int64)
-        self._hv["dec_bt2"] = self._hv["dec_bt"].reshape(S_, self.MB)
-        self._hv["pf_bt2"] = self._hv["pf_bt"].reshape(S_, self.MB)
-        base = self.dbuf.data_ptr()
-        self._dp = {k: base + 4 * o for k, (o, n) in self._off.items()}
 
         # ---- GEMM plans (TMA descriptors) --------------------------------------------------------
         self.plans = []
@@ -169,18 +175,44 @@ class ModelRunner:
         self.k_cache = torch.zeros(L, nb, Hkv, self.bs, D, dtype=bf, device=dev)
         self.v_cache = torch.zeros(L, nb, Hkv, self.bs, D, dtype=bf, device=dev)
 
-        self._graphs: Dict[Tuple[int, int, bool], torch.cuda.CUDAGraph] = {}
-        self._graph_launches: Dict[Tuple[int, int, bool], int] = {}
-        self.stream = torch.cuda.Stream(device=dev)   # every launch and copy of this runner
-        self._h2d_done = torch.cuda.Event()
-        self.flags = (_cabi.FLAG_PDL if e.use_pdl else 0) | (_cabi.FLAG_ORDERED if e.deterministic else 0)
         self.scale = float(m.head_dim) ** -0.5
-        self.launches_last_step = 0
-        self.kernel_launches = 0  # cumulative count of our kernels launched (graph replays included)
-        self.h2d_bytes = 0
-        self.d2h_bytes = 0
-        # bench hook: when a list, every step appends (start_event, end_event, n_decode, prefill_tokens, ctx_sum)
-        self.step_events: Optional[list] = None
+
+    def _init_staging(self) -> None:
+        # ---- staged integer / float inputs: one pinned host mirror, one device buffer -----------
+        T, dev, i32 = self.Tmax, self.dev, torch.int32
+        S_, R_ = self.Smax, self.Rmax
+        off, self._off = 0, {}
+
+        def region(name: str, n: int) -> None:
+            nonlocal off
+            off = (off + 3) // 4 * 4  # 16-byte aligned regions
+            self._off[name] = (off, n)
+            off += n
+
+        for name, n in (("ids", T), ("pos", T), ("slots", T), ("dec_lens", S_), ("pf_cu", S_ + 1), ("pf_ctx", S_),
+                        ("rows", R_), ("steps", R_), ("temps", R_), ("top_p", R_), ("seeds", 2 * R_),
+                        ("dec_bt", S_ * self.MB), ("pf_bt", S_ * self.MB),
+                        # the step seen sequence by sequence (programs with recurrent mixers): row range, first
+                        # position and state slot of every sequence, the sequence of every row, one block table
+                        ("seq_start", S_), ("seq_count", S_), ("seq_pos0", S_), ("seq_slot", S_), ("tok_seq", T),
+                        ("seq_bt", S_ * self.MB)):
+            region(name, n)
+        self._meta_lo = self._off["dec_lens"][0]
+        self._meta_hi = self._off["seeds"][0] + self._off["seeds"][1]
+        self.hbuf = torch.zeros(off, dtype=i32).pin_memory()
+        self.dbuf = torch.zeros(off, dtype=i32, device=dev)
+        self.hnp = self.hbuf.numpy()
+        self._hv = {k: self.hnp[o:o + n] for k, (o, n) in self._off.items()}
+        self._hv["temps_f"] = self._hv["temps"].view(np.float32)
+        self._hv["top_p_f"] = self._hv["top_p"].view(np.float32)
+        self._hv["seeds_q"] = self._hv["seeds"].view(np.int64)
+        self._hv["dec_bt2"] = self._hv["dec_bt"].reshape(S_, self.MB)
+        self._hv["pf_bt2"] = self._hv["pf_bt"].reshape(S_, self.MB)
+        self._hv["seq_bt2"] = self._hv["seq_bt"].reshape(S_, self.MB)
+        self._seq_lo = self._off["seq_start"][0]
+        self._seq_hi = self._off["seq_slot"][0] + self._off["seq_slot"][1]
+        base = self.dbuf.data_ptr()
+        self._dp = {k: base + 4 * o for k, (o, n) in self._off.items()}
 
     # ----------------------------------------------------------------------------------------------
     def _ck(self, rc: int) -> None:
@@ -202,6 +234,8 @@ class ModelRunner:
         exchange the pairs (8 bytes per row and rank, one NCCL all-gather) and pick the best (atx_sample_merge):
         the same token on every rank, and the token the unsharded sampler draws. Only when a request asks for a
         nucleus (top_p < 1: `whole_rows`) are the rows themselves assembled (all-reduce of a zero-filled buffer)."""
+        if self.program is not None:
+            return self.program.forward(T, n_dec + n_pf, n_rows)
         lib, m, w, ck = self.lib, self.m, self.w, self._ck
         st = torch.cuda.current_stream().cuda_stream
         fl = self.flags
@@ -464,7 +498,7 @@ class ModelRunner:
         """KV partitions per sequence. Short-context decode attention is a latency chain (block table
         -> K/V rows -> softmax), so cut it short: ~64 tokens per CTA while the grid stays within a
         few waves (<= 16 CTAs of 128 threads per SM), power-of-two buckets for the graph cache."""
-        if n_dec == 0:
+        if n_dec == 0 or self.program is not None:
             return 1
         by_len = max(1, (max_len + 63) // 64)
         by_grid = max(1, (16 * 148) // max(1, n_dec * max(1, self.m.num_key_value_heads // self.tp)))
@@ -490,16 +524,17 @@ class ModelRunner:
         """Block until the step's sampled ids have reached the pinned host buffer."""
         if handle is None:
             return {}
-        sampling, n_dec, B, buf, ev = handle
+        sampling, buf, ev = handle
         if ev is None:
             return {}
         ev.synchronize()
         oh = self.out_host[buf].numpy()
-        out: Dict[int, int] = {}
-        for r, c in enumerate(sampling):
-            slot_r = r if r < n_dec else (B - n_dec) + r
-            out[c.seq.uid] = int(oh[slot_r])
-        return out
+        return {c.seq.uid: int(oh[slot_r]) for c, slot_r in sampling if c.samples}
+
+    def read_logits(self, n_rows: int) -> np.ndarray:
+        """fp32 logits of the last step's rows [n_rows, V] (rows in the order the step assigned: Chunk.want_rows)."""
+        self.stream.synchronize()
+        return self.logits[:n_rows].cpu().numpy()
 
     def _launch(self, plan: StepPlan, chained: bool):
         self._h2d_done.synchronize()  # the previous step's staging copies have left the pinned buffer
@@ -513,14 +548,15 @@ class ModelRunner:
             raise RuntimeError("step exceeds the runner's static capacity")
         # TP steps contain NCCL all-reduces: they capture fine (thread-local capture mode), but the graphs
         # must be dropped before the process group is destroyed (close()).
-        use_graph = self.e.enable_cuda_graphs and n_pf == 0 and _bucket(n_dec, _GRAPH_BUCKETS) is not None \
+        use_graph = self.e.enable_cuda_graphs and n_pf == 0 and self._graphs_ok and _bucket(n_dec, _GRAPH_BUCKETS) is not None \
             and _bucket(n_dec, _GRAPH_BUCKETS) <= self.Smax
         B = _bucket(n_dec, _GRAPH_BUCKETS) if use_graph else n_dec
         T = B + (T_real - n_dec)
 
         ids, pos, slots = hv["ids"], hv["pos"], hv["slots"]
-        rows: List[int] = []
-        sampling: List[Chunk] = []
+        rows: List[int] = []                       # batch row whose logits land in row slot len(rows)
+        sampling: List[Tuple[Chunk, int]] = []     # (chunk, row slot) of the rows that carry sampling parameters
+        seq_view = self.program is not None and getattr(self.program, "needs_seq_view", False)
         max_len = 0
         for i, c in enumerate(decs):
             s = c.seq
@@ -533,13 +569,19 @@ class ModelRunner:
             hv["dec_lens"][i] = p + 1
             max_len = max(max_len, p + 1)
             rows.append(i)
-            sampling.append(c)
+            sampling.append((c, i))
+            c.want_rows = [i] if c.want else []
+            if seq_view:
+                self._stage_seq(i, s, i, 1, p)
         for i in range(n_dec, B):  # graph padding: no KV write, empty attention, ignored sample
             ids[i] = 0
             pos[i] = 0
             slots[i] = -1
             hv["dec_lens"][i] = 0
             rows.append(i)
+            if seq_view:
+                hv["seq_count"][i] = 0
+                hv["tok_seq"][i] = -1
         o = B
         max_q = 0
         hv["pf_cu"][0] = 0
@@ -555,25 +597,29 @@ class ModelRunner:
             hv["pf_cu"][j + 1] = o - B + n
             hv["pf_ctx"][j] = a + n
             max_q = max(max_q, n)
+            if seq_view:
+                self._stage_seq(B + j, s, o, n, a)
+            if c.want is not None:
+                c.want_rows = list(range(len(rows), len(rows) + len(c.want)))
+                rows.extend(o + k for k in c.want)
             if c.samples:
+                sampling.append((c, len(rows)))
                 rows.append(o + n - 1)
-                sampling.append(c)
             o += n
         n_rows = len(rows)
+        if n_rows > self.Rmax:
+            raise RuntimeError(f"step asks for {n_rows} rows of logits; the runner holds {self.Rmax} (max_logit_rows)")
         hv["rows"][:n_rows] = rows
+        hv["temps_f"][:n_rows] = 0.0       # rows nobody samples from: arg-max, result ignored
+        hv["top_p_f"][:n_rows] = 1.0
         k = 0
-        for r, c in enumerate(sampling):
+        for c, slot_r in sampling:
             s = c.seq
-            # padded graph rows sit between decodes and prefill rows: map sampling index -> row slot
-            slot_r = r if r < n_dec else (B - n_dec) + r
             hv["temps_f"][slot_r] = s.params.temperature
             hv["top_p_f"][slot_r] = s.params.top_p
             hv["seeds_q"][slot_r] = s.seed
             hv["steps"][slot_r] = s.num_generated + (1 if chained else 0)  # the in-flight step adds one token
             k += 1
-        for i in range(n_dec, B):
-            hv["temps_f"][i] = 0.0
-            hv["top_p_f"][i] = 1.0
 
         # ---- host -> device (pinned, async on the compute stream) --------------------------------
         self._h2d("ids", T)
@@ -584,8 +630,13 @@ class ModelRunner:
         self.h2d_bytes += 4 * (hi - lo)
         if n_dec:
             self._h2d("dec_bt", n_dec * self.MB)
-        if n_pf:
+        if n_pf and not seq_view:
             self._h2d("pf_bt", n_pf * self.MB)
+        if seq_view:
+            self.dbuf[self._seq_lo:self._seq_hi].copy_(self.hbuf[self._seq_lo:self._seq_hi], non_blocking=True)
+            self.h2d_bytes += 4 * (self._seq_hi - self._seq_lo)
+            self._h2d("tok_seq", T)
+            self._h2d("seq_bt", (B + n_pf) * self.MB)
         if chained:
             o_ids, _ = self._off["ids"]
             self.dbuf[o_ids:o_ids + n_dec].copy_(self.out_ids[:n_dec], non_blocking=True)
@@ -620,7 +671,16 @@ class ModelRunner:
             self.d2h_bytes += 4 * n_rows
             ev = self._out_events[buf]
             ev.record()
-        return (sampling, n_dec, B, buf, ev)
+        return (sampling, buf, ev)
+
+    def _stage_seq(self, i: int, s, row0: int, count: int, pos0: int) -> None:
+        """Entry i of the per-sequence view of the step (programs that walk sequences: recurrent state, one table)."""
+        hv = self._hv
+        hv["seq_start"][i], hv["seq_count"][i], hv["seq_pos0"][i] = row0, count, pos0
+        hv["seq_slot"][i] = s.state_slot if s.state_slot is not None else 0
+        hv["tok_seq"][row0:row0 + count] = i
+        tbl = s.blocks.table
+        hv["seq_bt2"][i, :len(tbl)] = tbl
 
     def _capture(self, B: int, splits: int, whole_rows: bool = False) -> torch.cuda.CUDAGraph:
         """Capture one decode step for batch bucket B. Inputs already sit in dbuf; the warm-up run

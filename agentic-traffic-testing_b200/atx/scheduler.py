@@ -23,7 +23,7 @@ from collections import deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence as Seq, Tuple
 
-from .kv_cache import BlockAllocator, OutOfBlocks, SequenceBlocks
+from .kv_cache import BlockAllocator, OutOfBlocks, SequenceBlocks, StateSlotPool
 
 
 @dataclass
@@ -76,6 +76,7 @@ class Sequence:
         self.seed = params.seed if params.seed is not None else default_seed(request_id)
         self.num_preemptions = 0
         self.cached_prompt_tokens = 0               # prompt tokens served by the prefix cache
+        self.state_slot: Optional[int] = None       # slot of the recurrent state (models that carry one)
 
     @property
     def num_generated(self) -> int:
@@ -97,6 +98,8 @@ class Chunk:
     start: int          # first token position processed this step
     count: int          # number of tokens processed
     samples: bool       # the last token of the chunk produces the next token
+    want: Optional[List[int]] = None         # offsets inside the chunk whose logits the caller asked for
+    want_rows: Optional[List[int]] = None    # filled by the runner: rows of its logits buffer, in the order of `want`
 
 
 @dataclass
@@ -117,8 +120,9 @@ class StepPlan:
 
 class Scheduler:
     def __init__(self, allocator: BlockAllocator, max_num_seqs: int, max_num_batched_tokens: int, max_model_len: int,
-                 eos_token_ids: Seq[int] = ()):
+                 eos_token_ids: Seq[int] = (), state_slots: Optional[StateSlotPool] = None):
         self.alloc = allocator
+        self.slots = state_slots     # None: the model keeps no per-sequence state besides its pages
         self.max_num_seqs = max_num_seqs
         self.max_num_batched_tokens = max_num_batched_tokens
         self.max_model_len = max_model_len
@@ -148,11 +152,25 @@ class Scheduler:
         seq.state = SeqState.FINISHED
         seq.finish_reason = reason
         seq.blocks.release()
+        self._release_slot(seq)
+
+    def _release_slot(self, seq: Sequence) -> None:
+        if self.slots is not None and seq.state_slot is not None:
+            self.slots.release(seq.state_slot)
+            seq.state_slot = None
+
+    def _take_slot(self, seq: Sequence) -> bool:
+        """A state slot for a sequence about to run (recurrent models); False if none is free."""
+        if self.slots is None or seq.state_slot is not None:
+            return True
+        seq.state_slot = self.slots.acquire()
+        return seq.state_slot is not None
 
     def _preempt(self, seq: Sequence, plan: StepPlan) -> None:
         """Recompute-style preemption: drop the blocks, keep the tokens, go back to the queue head."""
         self.running.remove(seq)
         seq.blocks.release()
+        self._release_slot(seq)     # recomputed from position 0 later: the state restarts from zero with it
         seq.num_computed = 0
         seq.state = SeqState.WAITING
         seq.num_preemptions += 1
@@ -218,6 +236,8 @@ class Scheduler:
 
         while self.waiting and budget > 0 and len(self.running) < self.max_num_seqs and not plan.preempted:
             seq = self.waiting[0]
+            if self.slots is not None and seq.state_slot is None and self.slots.num_free == 0:
+                break   # every state slot is held by a running sequence
             if not seq.blocks.table:
                 cached = seq.blocks.match_prefix(seq.tokens)
                 seq.num_computed = cached
@@ -229,6 +249,7 @@ class Scheduler:
                     seq.num_computed = 0
                 break
             self.waiting.popleft()
+            self._take_slot(seq)
             seq.state = SeqState.RUNNING
             self.running.append(seq)
             budget -= used
@@ -244,6 +265,44 @@ class Scheduler:
                 self._preempt(self.running[-1], plan)
             return self._again(plan)
         return plan
+
+    # ---- a step the caller dictates ---------------------------------------------------------------------
+    def plan_explicit(self, portions: Seq[Tuple[Sequence, int, Optional[List[int]]]]) -> StepPlan:
+        """The step that runs exactly the given (sequence, token count, wanted offsets) portions, in place of
+        schedule(): replaying a recorded schedule, or teacher-forced evaluation. Sequences are admitted at their first
+        portion (pages and, for recurrent models, a state slot are taken here; OutOfBlocks / RuntimeError if the pools
+        cannot hold the step: nothing is preempted on the caller's behalf). A single token of a sequence that already
+        has computed positions rides with the decodes, everything else is a prompt chunk. Nothing samples."""
+        plan = StepPlan()
+        for seq, count, want in portions:
+            if count <= 0 or seq.num_computed + count > len(seq.tokens):
+                raise ValueError(f"{seq.request_id}: portion of {count} tokens at {seq.num_computed} of {len(seq.tokens)}")
+            if seq.state is SeqState.FINISHED:
+                raise ValueError(f"{seq.request_id} has finished")
+            if seq.state is SeqState.WAITING:
+                if len(self.running) >= self.max_num_seqs:
+                    raise RuntimeError("more live sequences than max_num_seqs")
+                if not self._take_slot(seq):
+                    raise RuntimeError("no state slot free")
+                if seq in self.waiting:
+                    self.waiting.remove(seq)
+                seq.state = SeqState.RUNNING
+                self.running.append(seq)
+            seq.blocks.ensure_capacity(seq.num_computed + count)
+            chunk = Chunk(seq, seq.num_computed, count, False, want=list(want or []))
+            (plan.decodes if count == 1 and seq.num_computed > 0 else plan.prefills).append(chunk)
+        if plan.num_tokens > self.max_num_batched_tokens:
+            raise RuntimeError(f"step of {plan.num_tokens} tokens exceeds max_num_batched_tokens")
+        return plan
+
+    def retire(self, seq: Sequence, reason: str = "stop") -> None:
+        """End a sequence on the caller's word; its pages and state slot go back to the pools."""
+        if seq in self.running:
+            self.running.remove(seq)
+        if seq in self.waiting:
+            self.waiting.remove(seq)
+        if seq.state is not SeqState.FINISHED:
+            self._finish(seq, reason)
 
     def _retire_oversized(self, seq: Sequence, plan: StepPlan) -> None:
         if seq in self.running:

@@ -1,0 +1,283 @@
+// Softmax attention over the paged KV cache with the options the Llama path does not have: biases on q/k/v, an RMS norm
+// over the whole q (and k) projection, rotation of the first `rot_dims` dimensions of a head in adjacent pairs,
+// a tanh cap on the scores, a block-local causal mask (a query sees the keys of its own block of `chunk` positions),
+// a zero-score sink in the softmax denominator, a sigmoid gate per head on the output, any head sizes (the value size
+// may differ from the query/key size). One kernel serves prompt portions and single decoded tokens: a warp owns one
+// (row, head) and walks the keys of its block 32 at a time; scores, softmax and accumulation are fp32.
+// Cache element type XT = bf16 or fp32. Pages hold `bs` tokens: K [blocks, G, bs, D], V [blocks, G, bs, Vd].
+#include "common.cuh"
+
+#include "../../include/atx_b200.h"
+
+namespace atx {
+
+template <typename XT>
+__device__ __forceinline__ float ldx(const XT* p, long long i);
+template <>
+__device__ __forceinline__ float ldx<float>(const float* p, long long i) {
+    return p[i];
+}
+template <>
+__device__ __forceinline__ float ldx<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+    return __bfloat162float(p[i]);
+}
+__device__ __forceinline__ void stx(float* p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void stx(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+// ---- bias, whole-projection RMS norm, partial rotation, page scatter ----------------------------------------------
+// One block per row. rot: [max_pos, rot_dims] fp32, cos of the rot_dims/2 angles then their sines.
+template <typename XT>
+__global__ void __launch_bounds__(256)
+qk_prepare_kernel(const float* __restrict__ proj, long long ld, int q_off, int k_off, int v_off,
+                  const XT* __restrict__ bq, const XT* __restrict__ bk, const XT* __restrict__ bv,
+                  const XT* __restrict__ wq, const XT* __restrict__ wk, const float* __restrict__ rot, int rot_dims,
+                  const int* __restrict__ positions, const int* __restrict__ slots, XT* __restrict__ q_out,
+                  XT* __restrict__ k_cache, XT* __restrict__ v_cache, int H, int G, int D, int Vd, int bs, float eps) {
+    extern __shared__ float sm[];
+    __shared__ float red[2][32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int slot = slots[t];
+    if (slot < 0) return;  // padded row
+    const int nq = H * D, nk = G * D;
+    float* sq = sm;
+    float* sk = sm + nq;
+    const float* row = proj + t * ld;
+    float ssq = 0.f, ssk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+        float v = row[q_off + i];
+        if (bq) v += ldx(bq, i);
+        sq[i] = v;
+        ssq += v * v;
+    }
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+        float v = row[k_off + i];
+        if (bk) v += ldx(bk, i);
+        sk[i] = v;
+        ssk += v * v;
+    }
+    ssq = warp_sum(ssq);
+    ssk = warp_sum(ssk);
+    if ((threadIdx.x & 31) == 0) {
+        red[0][threadIdx.x >> 5] = ssq;
+        red[1][threadIdx.x >> 5] = ssk;
+    }
+    __syncthreads();
+    float tq = 0.f, tk = 0.f;
+    for (int i = 0; i < (blockDim.x >> 5); ++i) {
+        tq += red[0][i];
+        tk += red[1][i];
+    }
+    const float rq = wq ? rsqrtf(tq / static_cast<float>(nq) + eps) : 1.f;
+    const float rk = wk ? rsqrtf(tk / static_cast<float>(nk) + eps) : 1.f;
+    const int pos = positions[t];
+    const float* cs = rot + static_cast<long long>(pos) * rot_dims;
+    const int half = rot_dims / 2;
+    const int blk = slot / bs, off = slot - blk * bs;
+    // q and k: work items are pairs of adjacent dimensions
+    for (int e = threadIdx.x; e < (nq + nk) / 2; e += blockDim.x) {
+        const bool isq = e < nq / 2;
+        const int p = isq ? e : e - nq / 2;  // pair index inside q or k
+        const int i0 = 2 * p;
+        const int head = i0 / D, d = i0 - head * D;
+        float a, b;
+        if (isq) {
+            a = sq[i0] * rq;
+            b = sq[i0 + 1] * rq;
+            if (wq) {
+                a *= ldx(wq, i0);
+                b *= ldx(wq, i0 + 1);
+            }
+        } else {
+            a = sk[i0] * rk;
+            b = sk[i0 + 1] * rk;
+            if (wk) {
+                a *= ldx(wk, i0);
+                b *= ldx(wk, i0 + 1);
+            }
+        }
+        if (d < rot_dims) {
+            const float c = cs[d / 2], s = cs[half + d / 2];
+            const float ra = a * c - b * s, rb = b * c + a * s;
+            a = ra;
+            b = rb;
+        }
+        if (isq) {
+            stx(q_out, t * nq + i0, a);
+            stx(q_out, t * nq + i0 + 1, b);
+        } else {
+            const long long base = ((static_cast<long long>(blk) * G + head) * bs + off) * D + d;
+            stx(k_cache, base, a);
+            stx(k_cache, base + 1, b);
+        }
+    }
+    for (int i = threadIdx.x; i < G * Vd; i += blockDim.x) {
+        const int head = i / Vd, d = i - head * Vd;
+        float v = row[v_off + i];
+        if (bv) v += ldx(bv, i);
+        stx(v_cache, ((static_cast<long long>(blk) * G + head) * bs + off) * Vd + d, v);
+    }
+}
+
+// ---- attention ---------------------------------------------------------------------------------------------------
+constexpr int kMaxVdPerLane = 8;  // Vd <= 256
+
+template <typename XT>
+__global__ void __launch_bounds__(128)
+attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, const XT* __restrict__ v_cache,
+                  const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ tok_seq,
+                  const int* __restrict__ positions, const float* __restrict__ gate, long long ldg,
+                  XT* __restrict__ out, long long ldo, int H, int G, int D, int Vd, int bs, float scale, float softcap,
+                  int chunk, int sink, float out_scale) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long t = blockIdx.x;
+    const int h = blockIdx.y * 4 + warp;
+    const int s = tok_seq[t];
+    if (s < 0 || h >= H) return;
+    const int g = h / (H / G);
+    const int pos = positions[t];
+    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    float* sq = sm + warp * D;
+    for (int d = lane; d < D; d += 32) sq[d] = ldx(q, (t * H + h) * D + d) * scale;
+    __syncwarp();
+    const int* bt = block_tables + static_cast<long long>(s) * max_blocks;
+    // the sink is a key with score 0 and no value: the running maximum starts at 0 and the denominator at 1
+    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
+    float acc[kMaxVdPerLane];
+#pragma unroll
+    for (int i = 0; i < kMaxVdPerLane; ++i) acc[i] = 0.f;
+    for (int k0 = lo; k0 <= pos; k0 += 32) {
+        const int kp = k0 + lane;
+        float sc = -INFINITY;
+        long long vbase = 0;
+        if (kp <= pos) {
+            const int blk = bt[kp / bs];
+            const long long tokslot = (static_cast<long long>(blk) * G + g) * bs + (kp % bs);
+            const XT* kr = k_cache + tokslot * D;
+            vbase = tokslot * Vd;
+            float dot = 0.f;
+            for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldx(kr, d), dot);
+            sc = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
+        }
+        const float mt = fmaxf(m, warp_max(sc));
+        const float corr = (m == -INFINITY) ? 0.f : expf(m - mt);
+        const float p = (kp <= pos) ? expf(sc - mt) : 0.f;
+        l = l * corr + warp_sum(p);
+#pragma unroll
+        for (int i = 0; i < kMaxVdPerLane; ++i) acc[i] *= corr;
+        m = mt;
+        const int nk = min(32, pos - k0 + 1);
+        for (int j = 0; j < nk; ++j) {
+            const float pj = __shfl_sync(0xffffffffu, p, j);
+            const long long vb = __shfl_sync(0xffffffffu, vbase, j);
+#pragma unroll
+            for (int i = 0; i < kMaxVdPerLane; ++i) {
+                const int d = lane + 32 * i;
+                if (d < Vd) acc[i] = fmaf(pj, ldx(v_cache, vb + d), acc[i]);
+            }
+        }
+    }
+    float gmul = out_scale / l;
+    if (gate) gmul *= 1.f / (1.f + expf(-gate[t * ldg + h]));
+#pragma unroll
+    for (int i = 0; i < kMaxVdPerLane; ++i) {
+        const int d = lane + 32 * i;
+        if (d < Vd) stx(out, t * ldo + static_cast<long long>(h) * Vd + d, acc[i] * gmul);
+    }
+}
+
+}  // namespace atx
+
+using namespace atx;
+
+extern "C" {
+
+int atx_qk_prepare(const float* proj, long long ld, int q_off, int k_off, int v_off, const void* bq, const void* bk,
+                   const void* bv, const void* wq, const void* wk, const float* rot, int rot_dims, const int* positions,
+                   const int* slots, void* q_out, void* k_cache, void* v_cache, int T, int H, int G, int D, int Vd,
+                   int block_size, float eps, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(proj && positions && slots && q_out && k_cache && v_cache, "atx_qk_prepare: null pointer");
+    ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && D % 2 == 0 && Vd > 0 && block_size > 0,
+                "atx_qk_prepare: bad shape T=%d H=%d G=%d D=%d Vd=%d", T, H, G, D, Vd);
+    ATX_REQUIRE(rot_dims >= 0 && rot_dims % 2 == 0 && rot_dims <= D && (rot_dims == 0 || rot),
+                "atx_qk_prepare: rot_dims=%d must be even, at most D=%d, with a table", rot_dims, D);
+    const size_t smem = sizeof(float) * static_cast<size_t>(H + G) * D;
+    ATX_REQUIRE(smem <= 160 * 1024, "atx_qk_prepare: (H + G) * D = %d too large", (H + G) * D);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    if (flags & ATX_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (dtype == ATX_DT_F32) {
+        if (smem > 48 * 1024)
+            ATX_CUDA(cudaFuncSetAttribute(qk_prepare_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, qk_prepare_kernel<float>, proj, ld, q_off, k_off, v_off,
+                                    reinterpret_cast<const float*>(bq), reinterpret_cast<const float*>(bk),
+                                    reinterpret_cast<const float*>(bv), reinterpret_cast<const float*>(wq),
+                                    reinterpret_cast<const float*>(wk), rot, rot_dims, positions, slots,
+                                    reinterpret_cast<float*>(q_out), reinterpret_cast<float*>(k_cache),
+                                    reinterpret_cast<float*>(v_cache), H, G, D, Vd, block_size, eps));
+    } else {
+        using B = __nv_bfloat16;
+        if (smem > 48 * 1024)
+            ATX_CUDA(cudaFuncSetAttribute(qk_prepare_kernel<B>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, qk_prepare_kernel<B>, proj, ld, q_off, k_off, v_off,
+                                    reinterpret_cast<const B*>(bq), reinterpret_cast<const B*>(bk),
+                                    reinterpret_cast<const B*>(bv), reinterpret_cast<const B*>(wq),
+                                    reinterpret_cast<const B*>(wk), rot, rot_dims, positions, slots,
+                                    reinterpret_cast<B*>(q_out), reinterpret_cast<B*>(k_cache),
+                                    reinterpret_cast<B*>(v_cache), H, G, D, Vd, block_size, eps));
+    }
+    return ATX_OK;
+}
+
+int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
+                   const int* tok_seq, const int* positions, const float* gate, long long ldg, void* out, long long ldo,
+                   int T, int H, int G, int D, int Vd, int block_size, float scale, float softcap, int chunk, int sink,
+                   float out_scale, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_local: null pointer");
+    ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Vd > 0 && Vd <= 32 * kMaxVdPerLane && block_size > 0 &&
+                    chunk >= 0,
+                "atx_attn_local: bad shape T=%d H=%d G=%d D=%d Vd=%d (Vd <= %d)", T, H, G, D, Vd, 32 * kMaxVdPerLane);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T, (H + 3) / 4);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = sizeof(float) * 4 * static_cast<size_t>(D);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    if (flags & ATX_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    if (dtype == ATX_DT_F32) {
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_kernel<float>, reinterpret_cast<const float*>(q),
+                                    reinterpret_cast<const float*>(k_cache), reinterpret_cast<const float*>(v_cache),
+                                    block_tables, max_blocks, tok_seq, positions, gate, ldg,
+                                    reinterpret_cast<float*>(out), ldo, H, G, D, Vd, block_size, scale, softcap, chunk,
+                                    sink, out_scale));
+    } else {
+        using B = __nv_bfloat16;
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_kernel<B>, reinterpret_cast<const B*>(q),
+                                    reinterpret_cast<const B*>(k_cache), reinterpret_cast<const B*>(v_cache), block_tables,
+                                    max_blocks, tok_seq, positions, gate, ldg, reinterpret_cast<B*>(out), ldo, H, G, D,
+                                    Vd, block_size, scale, softcap, chunk, sink, out_scale));
+    }
+    return ATX_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,532 @@
+// Kernels of the sequence mixers that carry a recurrent state, and the glue around them:
+//   * residual update with a norm on both sides of the sublayer (post-norm of the sublayer's output, add, pre-norm of
+//     the next sublayer's input) in one pass over the row,
+//   * the decayed outer-product recurrence  S_t = a_t S_(t-1) + (c_t k_t) v_t^T,  y_t = S_t^T q_t (+ d v_t)  that both
+//     linear attention with a fixed decay per head and the selective state-space scan are instances of,
+//   * the short causal convolution with its carried inputs, the step size / decay of the selective scan,
+//   * gated RMS norms of mixer outputs (gate before or after the norm, norm in equal groups),
+//   * gate * up activation, embedding rows, [x ; x0] concatenation for a re-entrant block of layers.
+// Activations that feed a GEMM (and weights) are `XT` = bf16 or fp32; everything else is fp32. States are fp32.
+// A step is a flat batch of rows; sequence s owns rows [seq_start[s], seq_start[s] + seq_count[s]) whose first row is
+// position seq_pos0[s]; its states live in slot seq_slot[s]. A sequence at position 0 starts from zero state without
+// the slot being cleared first (slots are reused). seq_count 0 marks a padded entry.
+#include "common.cuh"
+
+#include "../../include/atx_b200.h"
+
+namespace atx {
+
+template <typename XT>
+__device__ __forceinline__ float ldf(const XT* p, long long i);
+template <>
+__device__ __forceinline__ float ldf<float>(const float* p, long long i) {
+    return p[i];
+}
+template <>
+__device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long long i) {
+    return __bfloat162float(p[i]);
+}
+__device__ __forceinline__ void stf(float* p, long long i, float v) { p[i] = v; }
+__device__ __forceinline__ void stf(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
+__device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
+
+static void set_pdl2(cudaLaunchConfig_t& cfg, cudaLaunchAttribute* attr, int flags) {
+    if (flags & ATX_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+}
+
+// block-wide sum; every thread gets the result. red: >= 32 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();  // red may still be read from a previous call
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float t = 0.f;
+    const int nw = (blockDim.x + 31) >> 5;
+    for (int i = 0; i < nw; ++i) t += red[i];
+    return t;
+}
+
+// ---- embedding rows -------------------------------------------------------------------------------------------
+template <typename XT>
+__global__ void __launch_bounds__(128) embed_rows_kernel(const int* __restrict__ ids, const XT* __restrict__ table,
+                                                         float* __restrict__ out, int W, int V) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    for (int i = threadIdx.x; i < W; i += blockDim.x)
+        out[static_cast<long long>(t) * W + i] = ldf(table, static_cast<long long>(id) * W + i);
+}
+
+// ---- [x ; x0]: the input of the projection that re-enters a block of layers ---------------------------------------
+template <typename XT>
+__global__ void __launch_bounds__(128) concat_embed_kernel(const float* __restrict__ h, const int* __restrict__ ids,
+                                                           const XT* __restrict__ table, XT* __restrict__ out, int W,
+                                                           int V) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    int id = ids[t];
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    XT* o = out + static_cast<long long>(t) * 2 * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        stf(o, i, h[static_cast<long long>(t) * W + i]);
+        o[W + i] = table[static_cast<long long>(id) * W + i];
+    }
+}
+
+// ---- residual update between two norms ---------------------------------------------------------------------------
+// h[r] += rms(y[r]) * w_post (if y) + vec (if vec);  out[t] = rms(h[r]) * w_pre (if w_pre);  r = rows ? rows[t] : t.
+// With `rows` the residual itself is left untouched (the gathered rows feed the LM head only).
+template <typename XT>
+__global__ void __launch_bounds__(256)
+resid_norm_kernel(float* __restrict__ h, const float* __restrict__ y, const XT* __restrict__ w_post,
+                  const XT* __restrict__ vec, const XT* __restrict__ w_pre, XT* __restrict__ out,
+                  const int* __restrict__ rows, int W, float eps) {
+    extern __shared__ float srow[];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const long long r = rows ? rows[t] : t;
+    float* hr = h + r * W;
+    float rs_y = 0.f;
+    if (y) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < W; i += blockDim.x) {
+            const float v = y[r * W + i];
+            srow[i] = v;
+            ss += v * v;
+        }
+        rs_y = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
+    }
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = hr[i];
+        if (y) v += srow[i] * rs_y * ldf(w_post, i);
+        if (vec) v += ldf(vec, i);
+        if ((y || vec) && !rows) hr[i] = v;
+        srow[i] = v;
+        ss += v * v;
+    }
+    if (!w_pre) return;
+    const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
+    XT* o = out + static_cast<long long>(t) * W;
+    for (int i = threadIdx.x; i < W; i += blockDim.x) stf(o, i, srow[i] * rs * ldf(w_pre, i));
+}
+
+// ---- act(gate) * up --------------------------------------------------------------------------------------------------
+template <typename XT>
+__global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict__ gu, XT* __restrict__ out, long long total,
+                                                        int I) {
+    pdl_launch_dependents();
+    pdl_wait();
+    for (long long e = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; e < total;
+         e += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const long long t = e / I;
+        const int i = static_cast<int>(e - t * I);
+        const float g = gu[t * 2 * I + i], u = gu[t * 2 * I + I + i];
+        stf(out, e, silu_f(g) * u);
+    }
+}
+
+// ---- gated RMS norm of a mixer's output --------------------------------------------------------------------------
+// mode 0: out = rms(y) * w * sigmoid(g) * scale      (gate after the norm)
+// mode 1: u = y * silu(g); out = rms(u) * w * scale  (gate before the norm)
+// The norm runs over n / groups consecutive elements; grid (T, groups).
+template <typename XT>
+__global__ void __launch_bounds__(256)
+gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ gate, long long ldg,
+                  const XT* __restrict__ w, XT* __restrict__ out, long long ldo, int n_group, float eps, int mode,
+                  float scale) {
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int c0 = blockIdx.y * n_group;
+    const float* yr = y + t * ldy + c0;
+    const float* gr = gate + t * ldg + c0;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < n_group; i += blockDim.x) {
+        float v = yr[i];
+        if (mode == 1) v *= silu_f(gr[i]);
+        ss += v * v;
+    }
+    const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(n_group) + eps);
+    XT* o = out + t * ldo + c0;
+    for (int i = threadIdx.x; i < n_group; i += blockDim.x) {
+        float v = yr[i];
+        if (mode == 1)
+            v = v * silu_f(gr[i]) * rs * ldf(w, c0 + i);
+        else
+            v = v * rs * ldf(w, c0 + i) * sigmoid_f(gr[i]);
+        stf(o, i, v * scale);
+    }
+}
+
+// ---- short causal convolution + silu, step size and decay of the selective scan -------------------------------------
+// Channel c of row t: out = silu(b[c] + sum_j w[c][j] * in[row(t) - (K-1-j)]), the last tap being the row itself. Inputs
+// before the step's first row come from the carried window conv_state[slot][K-1][C] (raw inputs of the last K-1
+// positions), inputs before position 0 are zero. Columns [C, C + H) of the same launch compute, per head,
+// dt = softplus(raw + dt_bias) and the decay exp(-exp(A_log) * dt).
+template <typename XT>
+__global__ void __launch_bounds__(256)
+conv_dt_kernel(const float* __restrict__ in, long long ld, int x_off, int dt_off, const XT* __restrict__ w,
+               const XT* __restrict__ b, const XT* __restrict__ dt_bias, const XT* __restrict__ a_log,
+               const float* __restrict__ conv_state, float* __restrict__ xbc, float* __restrict__ dt_out,
+               float* __restrict__ decay_out, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+               const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int C, int H, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int s = tok_seq[t];
+    if (s < 0) return;
+    const int i = static_cast<int>(t) - seq_start[s];
+    const int pos0 = seq_pos0[s];
+    const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
+    for (int c = threadIdx.x; c < C + H; c += blockDim.x) {
+        if (c < C) {
+            float acc = ldf(b, c);
+            for (int j = 0; j < K; ++j) {
+                const int rel = i - (K - 1 - j);
+                float v = 0.f;
+                if (rel >= 0)
+                    v = in[(t - i + rel) * ld + x_off + c];
+                else if (pos0 + rel >= 0)
+                    v = st[static_cast<long long>(K - 1 + rel) * C + c];
+                acc = fmaf(ldf(w, static_cast<long long>(c) * K + j), v, acc);
+            }
+            xbc[t * C + c] = silu_f(acc);
+        } else {
+            const int hh = c - C;
+            const float z = in[t * ld + dt_off + hh] + ldf(dt_bias, hh);
+            const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));  // softplus, exact for every z
+            dt_out[t * H + hh] = dt;
+            decay_out[t * H + hh] = expf(-expf(ldf(a_log, hh)) * dt);
+        }
+    }
+}
+
+// The carried window after the step: the raw inputs of the sequence's last K-1 positions. One thread per channel walks
+// the window front to back, so that a step shorter than the window shifts it in place.
+__global__ void __launch_bounds__(256)
+conv_state_update_kernel(const float* __restrict__ in, long long ld, int x_off, float* __restrict__ conv_state,
+                         const int* __restrict__ seq_start, const int* __restrict__ seq_count,
+                         const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int C, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x;
+    const int n = seq_count[s];
+    if (n <= 0) return;
+    const int pos0 = seq_pos0[s];
+    const long long r0 = seq_start[s];
+    float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C; c += gridDim.y * blockDim.x) {
+        for (int i = 0; i < K - 1; ++i) {
+            const int src = i + n;  // index into [old window | this step's rows]
+            float v;
+            if (src < K - 1)
+                v = (pos0 - (K - 1) + src >= 0) ? st[static_cast<long long>(src) * C + c] : 0.f;
+            else
+                v = in[(r0 + src - (K - 1)) * ld + x_off + c];
+            st[static_cast<long long>(i) * C + c] = v;
+        }
+    }
+}
+
+// ---- decayed outer-product recurrence ----------------------------------------------------------------------------
+// Per head: S_t = a_t S_(t-1) + (c_t k_t) v_t^T (S is D x V), y_t = S_t^T q_t + d v_t.
+//   a_t = decay_head[h] or decay_tok[t, h];  c_t = kscale_tok[t, h] or 1;  d = skip[h] or 0;
+//   q and k of head h are read from group h / (H / G) (G = H: a q/k per head), v from head h;
+//   act = 1 applies silu to q, k and v as they are read.
+// One CTA owns a V-tile of one head of one sequence and walks the sequence's rows in order. A thread keeps DS rows of
+// one column of S in registers for the whole walk (the state is read once and written once per step); rows are staged
+// through shared memory kChunk at a time, and the partial dot products of the D-slices are summed per chunk.
+constexpr int kRecChunk = 16;
+
+template <int DS>
+__global__ void __launch_bounds__(256)
+linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
+                         const float* __restrict__ v, long long ldv, int H, int G, int D, int V,
+                         const float* __restrict__ decay_head, const float* __restrict__ decay_tok,
+                         const float* __restrict__ kscale_tok, const float* __restrict__ skip, int act,
+                         float* __restrict__ state, float* __restrict__ y, long long ldy,
+                         const int* __restrict__ seq_start, const int* __restrict__ seq_count,
+                         const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int VT, int DG) {
+    extern __shared__ float sm[];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y;
+    const int n = seq_count[s];
+    if (n <= 0) return;
+    const long long r0 = seq_start[s];
+    const int g = h / (H / G);
+    const int tv = threadIdx.x % VT, dg = threadIdx.x / VT;
+    const int col = blockIdx.z * VT + tv;
+    const bool live = col < V && dg < DG;
+    const int d0 = dg * DS;
+    float* sq = sm;                            // [kRecChunk][D]
+    float* sk = sq + kRecChunk * D;            // [kRecChunk][D]   (already scaled by c_t)
+    float* sv = sk + kRecChunk * D;            // [kRecChunk][VT]
+    float* sa = sv + kRecChunk * VT;           // [kRecChunk]
+    float* sp = sa + kRecChunk;                // [kRecChunk][DG][VT] partial outputs
+    float S[DS];
+    float* st = state + ((static_cast<long long>(seq_slot[s]) * H + h) * D) * V;
+    const bool fresh = seq_pos0[s] == 0;
+#pragma unroll
+    for (int i = 0; i < DS; ++i) S[i] = (live && !fresh && d0 + i < D) ? st[static_cast<long long>(d0 + i) * V + col] : 0.f;
+    const float dskip = skip ? skip[h] : 0.f;
+    for (int c0 = 0; c0 < n; c0 += kRecChunk) {
+        const int cn = min(kRecChunk, n - c0);
+        __syncthreads();
+        for (int e = threadIdx.x; e < cn * D; e += blockDim.x) {
+            const int i = e / D, d = e - i * D;
+            const long long row = r0 + c0 + i;
+            float qv = q[row * ldq + g * D + d], kv = k[row * ldk + g * D + d];
+            if (act) {
+                qv = silu_f(qv);
+                kv = silu_f(kv);
+            }
+            if (kscale_tok) kv *= kscale_tok[row * H + h];
+            sq[i * D + d] = qv;
+            sk[i * D + d] = kv;
+        }
+        for (int e = threadIdx.x; e < cn * VT; e += blockDim.x) {
+            const int i = e / VT, j = e - i * VT;
+            const int cc = blockIdx.z * VT + j;
+            float vv = cc < V ? v[(r0 + c0 + i) * ldv + h * V + cc] : 0.f;
+            if (act) vv = silu_f(vv);
+            sv[i * VT + j] = vv;
+        }
+        for (int i = threadIdx.x; i < cn; i += blockDim.x)
+            sa[i] = decay_tok ? decay_tok[(r0 + c0 + i) * H + h] : decay_head[h];
+        __syncthreads();
+        if (live) {
+            for (int i = 0; i < cn; ++i) {
+                const float a = sa[i], vv = sv[i * VT + tv];
+                const float* qi = sq + i * D + d0;
+                const float* ki = sk + i * D + d0;
+                float acc = 0.f;
+#pragma unroll
+                for (int d = 0; d < DS; ++d) {
+                    if (d0 + d < D) {
+                        S[d] = fmaf(a, S[d], ki[d] * vv);
+                        acc = fmaf(S[d], qi[d], acc);
+                    }
+                }
+                sp[(i * DG + dg) * VT + tv] = acc;
+            }
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < cn * VT; e += blockDim.x) {
+            const int i = e / VT, j = e - i * VT;
+            const int cc = blockIdx.z * VT + j;
+            if (cc >= V) continue;
+            float acc = dskip * sv[i * VT + j];
+            for (int z = 0; z < DG; ++z) acc += sp[(i * DG + z) * VT + j];
+            y[(r0 + c0 + i) * ldy + h * V + cc] = acc;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < DS; ++i)
+            if (d0 + i < D) st[static_cast<long long>(d0 + i) * V + col] = S[i];
+    }
+}
+
+}  // namespace atx
+
+using namespace atx;
+
+#define ATX_DISPATCH_XT(dtype, ...)                                  \
+    do {                                                             \
+        if ((dtype) == ATX_DT_F32) {                                 \
+            using XT = float;                                        \
+            __VA_ARGS__;                                             \
+        } else {                                                     \
+            using XT = __nv_bfloat16;                                \
+            __VA_ARGS__;                                             \
+        }                                                            \
+    } while (0)
+
+extern "C" {
+
+int atx_embed_rows(const int* ids, const void* table, float* out, int T, int W, int V, int dtype, int flags,
+                   atx_stream_t stream) {
+    ATX_REQUIRE(ids && table && out, "atx_embed_rows: null pointer");
+    ATX_REQUIRE(T > 0 && W > 0 && V > 0, "atx_embed_rows: bad shape T=%d W=%d V=%d", T, W, V);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T);
+    cfg.blockDim = dim3(128);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, embed_rows_kernel<XT>, ids,
+                                                       reinterpret_cast<const XT*>(table), out, W, V)));
+    return ATX_OK;
+}
+
+int atx_concat_embed(const float* h, const int* ids, const void* table, void* out, int T, int W, int V, int dtype,
+                     int flags, atx_stream_t stream) {
+    ATX_REQUIRE(h && ids && table && out, "atx_concat_embed: null pointer");
+    ATX_REQUIRE(T > 0 && W > 0 && V > 0, "atx_concat_embed: bad shape T=%d W=%d V=%d", T, W, V);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T);
+    cfg.blockDim = dim3(128);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, concat_embed_kernel<XT>, h, ids,
+                                                       reinterpret_cast<const XT*>(table), reinterpret_cast<XT*>(out),
+                                                       W, V)));
+    return ATX_OK;
+}
+
+int atx_resid_norm(float* h, const float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
+                   const int* rows, int T, int W, float eps, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(h, "atx_resid_norm: null pointer");
+    ATX_REQUIRE(T > 0 && W > 0 && W <= 12288, "atx_resid_norm: bad shape T=%d W=%d (W <= 12288)", T, W);
+    ATX_REQUIRE((y == nullptr) == (w_post == nullptr), "atx_resid_norm: y and w_post come together");
+    ATX_REQUIRE((w_pre == nullptr) == (out == nullptr), "atx_resid_norm: w_pre and out come together");
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T);
+    cfg.blockDim = dim3(256);
+    cfg.dynamicSmemBytes = static_cast<size_t>(W) * 4;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
+                               &cfg, resid_norm_kernel<XT>, h, y, reinterpret_cast<const XT*>(w_post),
+                               reinterpret_cast<const XT*>(vec), reinterpret_cast<const XT*>(w_pre),
+                               reinterpret_cast<XT*>(out), rows, W, eps)));
+    return ATX_OK;
+}
+
+int atx_gated_act(const float* gu, void* out, int T, int I, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(gu && out, "atx_gated_act: null pointer");
+    ATX_REQUIRE(T > 0 && I > 0, "atx_gated_act: bad shape T=%d I=%d", T, I);
+    const long long total = static_cast<long long>(T) * I;
+    long long blocks = (total + 255) / 256;
+    const long long cap = static_cast<long long>(num_sms()) * 16;
+    if (blocks > cap) blocks = cap;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_act_kernel<XT>, gu, reinterpret_cast<XT*>(out), total, I)));
+    return ATX_OK;
+}
+
+int atx_gated_norm(const float* y, long long ldy, const float* gate, long long ldg, const void* w, void* out,
+                   long long ldo, int T, int n, int groups, float eps, int mode, float scale, int dtype, int flags,
+                   atx_stream_t stream) {
+    ATX_REQUIRE(y && gate && w && out, "atx_gated_norm: null pointer");
+    ATX_REQUIRE(T > 0 && n > 0 && groups > 0 && n % groups == 0 && (mode == 0 || mode == 1),
+                "atx_gated_norm: bad arguments T=%d n=%d groups=%d mode=%d", T, n, groups, mode);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T, groups);
+    cfg.blockDim = dim3(256);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_kernel<XT>, y, ldy, gate, ldg,
+                                                       reinterpret_cast<const XT*>(w), reinterpret_cast<XT*>(out), ldo,
+                                                       n / groups, eps, mode, scale)));
+    return ATX_OK;
+}
+
+int atx_conv_dt(const float* in, long long ld, int x_off, int dt_off, const void* w, const void* b, const void* dt_bias,
+                const void* a_log, const float* conv_state, float* xbc, float* dt_out, float* decay_out,
+                const int* tok_seq, const int* seq_start, const int* seq_pos0, const int* seq_slot, int T, int C, int H,
+                int K, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(in && w && b && dt_bias && a_log && conv_state && xbc && dt_out && decay_out && tok_seq && seq_start &&
+                    seq_pos0 && seq_slot,
+                "atx_conv_dt: null pointer");
+    ATX_REQUIRE(T > 0 && C > 0 && H > 0 && K >= 1, "atx_conv_dt: bad shape T=%d C=%d H=%d K=%d", T, C, H, K);
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(T);
+    cfg.blockDim = dim3(256);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
+                               &cfg, conv_dt_kernel<XT>, in, ld, x_off, dt_off, reinterpret_cast<const XT*>(w),
+                               reinterpret_cast<const XT*>(b), reinterpret_cast<const XT*>(dt_bias),
+                               reinterpret_cast<const XT*>(a_log), conv_state, xbc, dt_out, decay_out, tok_seq,
+                               seq_start, seq_pos0, seq_slot, C, H, K)));
+    return ATX_OK;
+}
+
+int atx_conv_state_update(const float* in, long long ld, int x_off, float* conv_state, const int* seq_start,
+                          const int* seq_count, const int* seq_pos0, const int* seq_slot, int n_seqs, int C, int K,
+                          int flags, atx_stream_t stream) {
+    ATX_REQUIRE(in && conv_state && seq_start && seq_count && seq_pos0 && seq_slot, "atx_conv_state_update: null pointer");
+    ATX_REQUIRE(n_seqs > 0 && C > 0 && K >= 1, "atx_conv_state_update: bad shape n_seqs=%d C=%d K=%d", n_seqs, C, K);
+    if (K == 1) return ATX_OK;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(n_seqs, (C + 255) / 256);
+    cfg.blockDim = dim3(256);
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, conv_state_update_kernel, in, ld, x_off, conv_state, seq_start, seq_count, seq_pos0,
+                                seq_slot, C, K));
+    return ATX_OK;
+}
+
+int atx_linear_recurrence(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                          int H, int G, int D, int V, const float* decay_head, const float* decay_tok,
+                          const float* kscale_tok, const float* skip, int act, float* state, float* y, long long ldy,
+                          const int* seq_start, const int* seq_count, const int* seq_pos0, const int* seq_slot,
+                          int n_seqs, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k && v && state && y && seq_start && seq_count && seq_pos0 && seq_slot,
+                "atx_linear_recurrence: null pointer");
+    ATX_REQUIRE((decay_head != nullptr) != (decay_tok != nullptr),
+                "atx_linear_recurrence: exactly one of decay_head / decay_tok");
+    ATX_REQUIRE(n_seqs > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0 && D <= 512,
+                "atx_linear_recurrence: bad shape n_seqs=%d H=%d G=%d D=%d V=%d (D <= 512)", n_seqs, H, G, D, V);
+    const int DS = D > 256 ? 64 : 32;
+    const int DG = (D + DS - 1) / DS;
+    int VT = (256 / DG) / 32 * 32;
+    if (VT < 32) VT = 32;
+    const int v32 = (V + 31) / 32 * 32;
+    if (VT > v32) VT = v32;
+    const int threads = VT * DG;
+    const size_t smem = sizeof(float) * (static_cast<size_t>(kRecChunk) * (2 * D + VT + 1 + DG * VT));
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(n_seqs, H, (V + VT - 1) / VT);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = reinterpret_cast<cudaStream_t>(stream);
+    set_pdl2(cfg, attr, flags);
+    ATX_REQUIRE(smem <= 160 * 1024, "atx_linear_recurrence: D=%d needs %zu bytes of shared memory", D, smem);
+    if (DS == 32) {
+        if (smem > 48 * 1024)
+            ATX_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<32>, q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head,
+                                    decay_tok, kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0,
+                                    seq_slot, VT, DG));
+    } else {
+        if (smem > 48 * 1024)
+            ATX_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                          static_cast<int>(smem)));
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<64>, q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head,
+                                    decay_tok, kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0,
+                                    seq_slot, VT, DG));
+    }
+    return ATX_OK;
+}
+
+}  // extern "C"

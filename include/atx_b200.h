@@ -209,6 +209,74 @@ int atx_sample_shard(const float* logits, long long ldl, int idx_offset, const f
                      atx_stream_t stream);
 int atx_sample_merge(const void* pairs, int world, int B, int* out_ids, int flags, atx_stream_t stream);
 
+/* ---- Element type of weights, GEMM-input activations and KV pages in the calls below ------------------------------ */
+#define ATX_DT_BF16 0
+#define ATX_DT_F32 1
+
+/* out[t, n] (+)= sum_k X[t, k] * W[n, k] on the FMA pipe: fp32 operands (true 32-bit products), or shapes the tcgen05
+ * plan refuses (K not a multiple of 64). Any N, K, T and row pitches; fp32 accumulation in a fixed order. */
+int atx_gemm_simple(const void* W, long long ldw, const void* X, long long ldx, float* out, long long ldo, int T, int N,
+                    int K, int add, int dtype, int flags, atx_stream_t stream);
+
+/* ---- Mixers with a recurrent state, and what surrounds them ---------------------------------------------------------
+ * A step is a flat batch of rows. Sequence s owns rows [seq_start[s], seq_start[s] + seq_count[s]); its first row is
+ * position seq_pos0[s]; tok_seq[t] is the sequence of row t (-1: padded row); seq_slot[s] is the state slot. A sequence
+ * at position 0 starts from zero state whatever the slot held before. seq_count 0 marks a padded entry. */
+
+/* out[t, :] = table[ids[t], :] as fp32, any width. */
+int atx_embed_rows(const int* ids, const void* table, float* out, int T, int W, int V, int dtype, int flags,
+                   atx_stream_t stream);
+/* out[t, :] = [ h[t, :] rounded to the element type ; table[ids[t], :] ]  (2 W columns). */
+int atx_concat_embed(const float* h, const int* ids, const void* table, void* out, int T, int W, int V, int dtype,
+                     int flags, atx_stream_t stream);
+/* Residual update between two RMS norms, one pass over the row:
+ *   h[r] += rms(y[r]) * w_post  (if y)  + vec (if vec);   out[t] = rms(h[r]) * w_pre  (if w_pre);   r = rows ? rows[t] : t
+ * rms(x) = x / sqrt(mean(x^2) + eps). With `rows` the residual is read only. */
+int atx_resid_norm(float* h, const float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
+                   const int* rows, int T, int W, float eps, int dtype, int flags, atx_stream_t stream);
+/* out[t, i] = silu(gu[t, i]) * gu[t, I + i] */
+int atx_gated_act(const float* gu, void* out, int T, int I, int dtype, int flags, atx_stream_t stream);
+/* Gated RMS norm over n / groups consecutive elements at a time:
+ *   mode 0: out = rms(y) * w * sigmoid(gate) * scale;   mode 1: out = rms(y * silu(gate)) * w * scale */
+int atx_gated_norm(const float* y, long long ldy, const float* gate, long long ldg, const void* w, void* out,
+                   long long ldo, int T, int n, int groups, float eps, int mode, float scale, int dtype, int flags,
+                   atx_stream_t stream);
+/* Short causal convolution over C channels (taps K, last tap = the row itself) + bias + silu, with the raw inputs of the
+ * K - 1 positions before the step taken from conv_state [slots, K - 1, C]; and per head dt = softplus(in[dt_off + h] +
+ * dt_bias[h]), decay = exp(-exp(a_log[h]) * dt). xbc [T, C], dt_out / decay_out [T, H], all fp32. */
+int atx_conv_dt(const float* in, long long ld, int x_off, int dt_off, const void* w, const void* b, const void* dt_bias,
+                const void* a_log, const float* conv_state, float* xbc, float* dt_out, float* decay_out,
+                const int* tok_seq, const int* seq_start, const int* seq_pos0, const int* seq_slot, int T, int C, int H,
+                int K, int dtype, int flags, atx_stream_t stream);
+/* conv_state <- raw inputs of each sequence's last K - 1 positions (run after atx_conv_dt of the same step). */
+int atx_conv_state_update(const float* in, long long ld, int x_off, float* conv_state, const int* seq_start,
+                          const int* seq_count, const int* seq_pos0, const int* seq_slot, int n_seqs, int C, int K,
+                          int flags, atx_stream_t stream);
+/* Decayed outer-product recurrence per head, state fp32 [slots, H, D, V]:
+ *   S_t = a_t S_(t-1) + (c_t k_t) v_t^T,   y_t = S_t^T q_t + d v_t
+ * a_t = decay_head[h] or decay_tok[t, h]; c_t = kscale_tok[t, h] or 1; d = skip[h] or 0; q/k of head h come from group
+ * h / (H / G) at columns [group * D, ...), v and y from columns [h * V, ...); act = 1: silu on q, k, v as read. */
+int atx_linear_recurrence(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                          int H, int G, int D, int V, const float* decay_head, const float* decay_tok,
+                          const float* kscale_tok, const float* skip, int act, float* state, float* y, long long ldy,
+                          const int* seq_start, const int* seq_count, const int* seq_pos0, const int* seq_slot,
+                          int n_seqs, int flags, atx_stream_t stream);
+/* q/k/v of one step from a fused projection (fp32, row pitch ld, column offsets): + bias (nullable), RMS norm over the
+ * WHOLE q and the whole k projection with weights wq [H D] / wk [G D] (nullable: no norm), rotation of adjacent pairs
+ * (2i, 2i+1) of the first rot_dims dimensions of every head by the angles of table rot [max_pos, rot_dims] (cosines,
+ * then sines), q -> q_out [T, H D], k / v -> pages K [blocks, G, bs, D], V [blocks, G, bs, Vd] at slots[t]. */
+int atx_qk_prepare(const float* proj, long long ld, int q_off, int k_off, int v_off, const void* bq, const void* bk,
+                   const void* bv, const void* wq, const void* wk, const float* rot, int rot_dims, const int* positions,
+                   const int* slots, void* q_out, void* k_cache, void* v_cache, int T, int H, int G, int D, int Vd,
+                   int block_size, float eps, int dtype, int flags, atx_stream_t stream);
+/* Attention of every row over its sequence's pages: score = (q . k) * scale, capped as softcap * tanh(score / softcap)
+ * if softcap > 0; a query at position p sees keys j <= p with floor(j / chunk) == floor(p / chunk) (chunk 0: all j <= p);
+ * sink != 0 adds 1 to the softmax denominator; out = softmax . V * sigmoid(gate[t, h]) (gate nullable) * out_scale. */
+int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, const int* block_tables, int max_blocks,
+                   const int* tok_seq, const int* positions, const float* gate, long long ldg, void* out, long long ldo,
+                   int T, int H, int G, int D, int Vd, int block_size, float scale, float softcap, int chunk, int sink,
+                   float out_scale, int dtype, int flags, atx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
