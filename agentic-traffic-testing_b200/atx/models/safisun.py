@@ -377,7 +377,8 @@ def rotation_table(base: float, dims: int, max_pos: int, device: torch.device) -
 
 
 class Program:
-    needs_seq_view = True
+    needs_seq_view = True     # kernels walk the step sequence by sequence (ModelRunner._stage_seq)
+    graph_safe = True         # a sequence staged with no rows and no page slot is skipped by every stateful kernel
 
     def __init__(self, r) -> None:
         self.r = r

@@ -685,6 +685,16 @@ class ModelRunner:
     def _capture(self, B: int, splits: int, whole_rows: bool = False) -> torch.cuda.CUDAGraph:
         """Capture one decode step for batch bucket B. Inputs already sit in dbuf; the warm-up run
         writes the same K/V slots and logits the replay will write again, so it is harmless."""
+        stateful = self.program is not None
+        if stateful:
+            # A program with recurrent state must not run the step three times (warm-up, capture, replay): for the
+            # first two every sequence is staged as absent (no rows, no page slots), which its kernels skip; the
+            # real values go back in before the replay.
+            o, n = self._off["seq_count"]
+            self.dbuf[o:o + n].zero_()
+            for name in ("tok_seq", "slots"):
+                o, n = self._off[name]
+                self.dbuf[o:o + n].fill_(-1)
         torch.cuda.current_stream().synchronize()
         s = torch.cuda.Stream(device=self.dev)
         s.wait_stream(torch.cuda.current_stream())
@@ -697,6 +707,11 @@ class ModelRunner:
             n = self._forward(B, B, splits, 0, 0, B, whole_rows)
         self._graphs[(B, splits, whole_rows)] = g
         self._graph_launches[(B, splits, whole_rows)] = n
+        if stateful:
+            for name in ("seq_count", "tok_seq", "slots"):
+                o, k = self._off[name]
+                self.dbuf[o:o + k].copy_(self.hbuf[o:o + k], non_blocking=True)
+            self._h2d_done.record()   # the pinned buffer is read again here: the next step's staging waits for it
         return g
 
     def close(self) -> None:

@@ -1,0 +1,417 @@
+"""The Safisun family on the GPU against the float64 reference (oracle/safisun_ref.py): kernels alone on inputs built
+so that a lost key, a wrong block edge or a dropped state shows, and the engine (scheduler, pages, state slots,
+runner, kernels) on small random models: whole prompts, token-by-token decoding, portions, mixed batches, reuse of
+pages and slots, greedy generation through the ordinary entry point."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import safisun_ref as R
+
+pytestmark = pytest.mark.gpu
+F64 = torch.float64
+DEV = "cuda:0"
+
+
+# ---- small models ------------------------------------------------------------------------------------------------------
+
+def lightning_layer(heads=3, dim=8, vdim=12, mlp=None, decay=None):
+    return {"type": "lightning", "mlp": mlp,
+            "mixer": {"decay": decay or [0.5, 0.9, 0.995][:heads], "dim": dim, "heads": heads, "vdim": vdim}}
+
+
+def mamba_layer(heads=4, vdim=10, state=8, groups=2, norm_groups=2, conv=3, mlp=None):
+    return {"type": "mamba2", "mlp": mlp,
+            "mixer": {"conv": conv, "groups": groups, "heads": heads, "norm_groups": norm_groups, "state": state, "vdim": vdim}}
+
+
+def parallel_layer(mlp=None, size=8, rot_dims=8, dim=16, vdim=12, heads=4, kv=2):
+    return {"type": "parallel", "mlp": mlp,
+            "mixer": {"left": {"dim": dim, "heads": heads, "kv_heads": kv, "mask": {"size": size},
+                               "rot": {"base": 100.0, "dims": rot_dims}, "scale": 0.3, "softcap": 5.0, "vdim": vdim},
+                      "left_scale": 0.7, "right_scale": 1.3,
+                      "right": {"decay": [0.8, 0.97], "dim": 12, "heads": 2, "vdim": 6}}}
+
+
+def model_cfg(layers, width=64, vocab=96, loop=None):
+    return {"architecture": "Safisun", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": layers, "loop": loop}
+
+
+def loop_model(width=64):
+    ff = {"ff": 64, "kind": "dense"}
+    return model_cfg([lightning_layer(), mamba_layer(mlp={"ff": 40, "kind": "dense"}), parallel_layer(mlp=ff),
+                      lightning_layer(heads=2, dim=16, vdim=8, decay=[0.7, 0.999])],
+                     width=width, loop={"start": 1, "stop": 3, "times": 2})
+
+
+def engine(cfg, wt, dtype="float32", **kw):
+    from atx.config import EngineConfig, ModelSource
+    from atx.engine import LLMEngine
+    from atx.models import safisun
+
+    mcfg = safisun.Config.from_json(cfg)
+    xt = torch.float32 if dtype == "float32" else torch.bfloat16
+    w = safisun.Weights.from_state_dict(mcfg, wt, torch.device(DEV), xt)
+    ecfg = EngineConfig(max_model_len=kw.pop("max_model_len", 256), max_num_seqs=kw.pop("max_num_seqs", 4),
+                        max_num_batched_tokens=kw.pop("max_num_batched_tokens", 256),
+                        num_gpu_blocks=kw.pop("num_gpu_blocks", 64), enable_prefix_caching=False,
+                        enable_cuda_graphs=kw.pop("enable_cuda_graphs", False),
+                        async_scheduling=kw.pop("async_scheduling", False), dtype=dtype,
+                        max_logit_rows=kw.pop("max_logit_rows", 256), **kw)
+    return LLMEngine(ModelSource(mcfg, None, None), ecfg, w)
+
+
+def tokens(n, vocab=96, seed=0):
+    return [int(t) for t in torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed))]
+
+
+def rel(got, want):
+    """Worst row of rms(got - want) / rms(want), both with the row mean taken off."""
+    got, want = torch.as_tensor(got, dtype=F64), torch.as_tensor(want, dtype=F64)
+    d = got - want
+    d = d - d.mean(-1, keepdim=True)
+    w = want - want.mean(-1, keepdim=True)
+    return float((d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt()).max())
+
+
+TOL = {"float32": 2e-5, "bfloat16": 6e-2}
+
+
+def whole(eng, rid, toks, end=True):
+    return eng.feed([(rid, toks, list(range(len(toks))))], [rid] if end else [])
+
+
+# ---- each mechanism alone, through the engine ------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [64, 96])       # 96: not a multiple of the tensor-core GEMM's K block
+@pytest.mark.parametrize("kind", ["lightning", "mamba2", "parallel", "parallel_full", "lightning_ffn"])
+def test_one_layer_models(kind, width, dtype):
+    layer = {"lightning": lightning_layer(), "mamba2": mamba_layer(),
+             "parallel": parallel_layer(), "parallel_full": parallel_layer(size=None, rot_dims=16, kv=4),
+             "lightning_ffn": lightning_layer(heads=1, dim=4, vdim=4, decay=[0.9], mlp={"ff": 24, "kind": "dense"})}[kind]
+    if kind == "parallel_full":
+        layer["mixer"]["left"]["mask"] = None
+        layer["mixer"]["left"]["softcap"] = None
+    cfg = model_cfg([layer], width=width)
+    wt = R.random_checkpoint(cfg, 11)
+    toks = tokens(45, seed=1)
+    eng = engine(cfg, wt, dtype)
+    got = whole(eng, "a", toks)
+    assert rel(got, R.forward(cfg, wt, toks)) < TOL[dtype]
+
+
+def test_first_tokens_of_a_sequence():
+    cfg = loop_model()
+    wt = R.random_checkpoint(cfg, 3)
+    eng = engine(cfg, wt)
+    for n in (1, 2, 3):
+        toks = tokens(n, seed=n)
+        assert rel(whole(eng, f"r{n}", toks), R.forward(cfg, wt, toks)) < TOL["float32"]
+
+
+# ---- the same logits however the tokens are cut ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prefill_token_by_token_and_portions_agree(dtype):
+    cfg = loop_model()
+    wt = R.random_checkpoint(cfg, 4)
+    toks = tokens(70, seed=5)
+    want = R.forward(cfg, wt, toks)
+    eng = engine(cfg, wt, dtype)
+    a = whole(eng, "w", toks)
+    b = np.concatenate([eng.feed([("t", toks[i:i + 1], [0])], ["t"] if i == len(toks) - 1 else []) for i in range(len(toks))])
+    cuts, parts, at = [2, 3, 16, 1, 7, 2, 9, 1, 1, 17, 2], [], 0
+    cuts.append(len(toks) - sum(cuts))
+    for n in cuts:
+        parts.append(eng.feed([("p", toks[at:at + n], list(range(n)))], ["p"] if at + n == len(toks) else []))
+        at += n
+    c = np.concatenate(parts)
+    for got in (a, b, c):
+        assert rel(got, want) < TOL[dtype]
+    if dtype == "float32":
+        assert rel(b, a) < 1e-5 and rel(c, a) < 1e-5
+
+
+def test_long_decoding_keeps_its_state():
+    cfg = loop_model()
+    wt = R.random_checkpoint(cfg, 6)
+    toks = tokens(200, seed=7)
+    eng = engine(cfg, wt)
+    got = [eng.feed([("d", toks[:9], list(range(9)))], [])]
+    got += [eng.feed([("d", toks[i:i + 1], [0])], []) for i in range(9, len(toks))]
+    assert rel(np.concatenate(got), R.forward(cfg, wt, toks)) < TOL["float32"]
+
+
+def test_mixed_batches_equal_each_request_alone():
+    cfg = loop_model()
+    wt = R.random_checkpoint(cfg, 8)
+    reqs = {"a": tokens(61, seed=1), "b": tokens(23, seed=2), "c": tokens(40, seed=3), "d": tokens(5, seed=4)}
+    want = {k: R.forward(cfg, wt, v) for k, v in reqs.items()}
+    # portions of some requests beside single tokens of others; c joins late, d comes and goes in the middle
+    steps = [[("a", 17), ("b", 2)], [("a", 1), ("b", 19)], [("a", 30), ("b", 1), ("c", 3)], [("b", 1), ("c", 1), ("d", 5)],
+             [("a", 13), ("c", 20)], [("c", 1)], [("c", 15)]]
+    eng = engine(cfg, wt, max_num_seqs=4)
+    at = {k: 0 for k in reqs}
+    got = {k: [] for k in reqs}
+    for step in steps:
+        entries, end = [], []
+        for k, n in step:
+            entries.append((k, reqs[k][at[k]:at[k] + n], list(range(n))))
+            at[k] += n
+            if at[k] == len(reqs[k]):
+                end.append(k)
+        out = eng.feed(entries, end)
+        o = 0
+        for k, n in step:
+            got[k].append(out[o:o + n])
+            o += n
+    assert at == {k: len(v) for k, v in reqs.items()}
+    for k in reqs:
+        assert rel(np.concatenate(got[k]), want[k]) < TOL["float32"], k
+    assert eng.allocator.num_free == eng.allocator.num_blocks and eng.state_slots.num_free == 4
+
+
+def test_pages_and_slots_are_reused_without_leaking_state():
+    cfg = loop_model()
+    wt = R.random_checkpoint(cfg, 9)
+    eng = engine(cfg, wt, max_num_seqs=2, num_gpu_blocks=6, max_model_len=96)       # 96 tokens of pages, two slots
+    first = tokens(90, seed=1)
+    whole(eng, "big", first)                                   # fills every page and leaves a large state in slot 0
+    for seed, n in ((2, 33), (3, 50), (4, 17)):
+        toks = tokens(n, seed=seed)
+        assert rel(whole(eng, f"r{seed}", toks), R.forward(cfg, wt, toks)) < TOL["float32"]
+    # a request that starts while another is alive takes the freed slot and freed pages
+    a, b, c = tokens(40, seed=5), tokens(30, seed=6), tokens(36, seed=7)
+    ga = [eng.feed([("a", a[:20], list(range(20))), ("b", b, list(range(30)))], ["b"])]
+    gc = eng.feed([("a", a[20:21], [0]), ("c", c, list(range(36)))], ["c"])
+    ga += [gc[:1], eng.feed([("a", a[21:], list(range(19)))], ["a"])]
+    assert rel(np.concatenate(ga), R.forward(cfg, wt, a)) < TOL["float32"]
+    assert rel(gc[1:], R.forward(cfg, wt, c)) < TOL["float32"]
+    with pytest.raises(Exception):
+        eng.feed([("x", tokens(97, seed=8), [])], [])          # more pages than the pool has
+
+
+def test_other_sizes():
+    ff = {"ff": 72, "kind": "dense"}
+    cfg = model_cfg([mamba_layer(heads=6, vdim=4, state=20, groups=3, norm_groups=1, conv=5, mlp=ff),
+                     parallel_layer(size=5, rot_dims=2, dim=6, vdim=40, heads=6, kv=1),
+                     lightning_layer(heads=1, dim=40, vdim=3, decay=[0.93])],
+                    width=80, vocab=53, loop={"start": 0, "stop": 2, "times": 3})
+    wt = R.random_checkpoint(cfg, 12)
+    toks = tokens(37, vocab=53, seed=2)
+    want = R.forward(cfg, wt, toks)
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(cfg, wt, dtype)
+        got = np.concatenate([eng.feed([("s", toks[:20], list(range(20)))], []),
+                              eng.feed([("s", toks[20:22], [0, 1])], [])] +
+                             [eng.feed([("s", toks[i:i + 1], [0])], []) for i in range(22, 37)])
+        assert rel(got, want) < TOL[dtype], dtype
+
+
+# ---- generation through the ordinary entry point ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("mode", ["plain", "chunked_prefill", "async", "graphs"])
+def test_greedy_generation_matches_the_reference(mode):
+    from atx.scheduler import SamplingParams
+
+    cfg = loop_model()
+    wt = R.random_checkpoint(cfg, 13)
+    prompts = [tokens(37, seed=1), tokens(5, seed=2), tokens(64, seed=3)]
+    kw = {"plain": {}, "chunked_prefill": {"max_num_batched_tokens": 16}, "async": {"async_scheduling": True},
+          "graphs": {"async_scheduling": True, "enable_cuda_graphs": True}}[mode]
+    eng = engine(cfg, wt, **kw)
+    outs = eng.generate_sync(prompts, SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 12
+        lg = R.forward(cfg, wt, p + o[:-1])[len(p) - 1:]
+        top2 = lg.topk(2, dim=-1).values
+        for i, tok in enumerate(o):            # teacher-forced: every token is the reference's arg-max (ties aside)
+            assert tok == int(lg[i].argmax()) or float(top2[i, 0] - top2[i, 1]) < 1e-4, (mode, i)
+    assert eng.allocator.num_free == eng.allocator.num_blocks and eng.state_slots.num_free == eng.state_slots.num_slots
+
+
+# ---- kernels alone, on inputs where one wrong key or a lost state shows ----------------------------------------------------
+
+def _lib():
+    from atx import _cabi
+
+    return _cabi.load(), _cabi
+
+
+def _i32(x):
+    return torch.tensor(x, dtype=torch.int32, device=DEV)
+
+
+def _st():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("size,n", [(8, 41), (16, 50), (0, 37)])
+def test_attention_block_edges_with_dominant_keys(size, n):
+    """Every block's first and last key carry a score far above the rest and a value of their own: a query that sees
+    one key too many or too few lands on a different value. Rows are also run one at a time (decode form) over pages
+    in scrambled order."""
+    lib, cabi = _lib()
+    H, G, D, Vd, bs = 4, 2, 8, 6, 16
+    g = torch.Generator().manual_seed(size + n)
+    q = torch.randn(n, H, D, generator=g, dtype=F64)
+    k = 0.2 * torch.randn(n, G, D, generator=g, dtype=F64)
+    v = torch.randn(n, G, Vd, generator=g, dtype=F64)
+    edge = [j for j in range(n) if size and (j % size in (0, size - 1))] or [0, 5, n - 2]
+    for j in edge:
+        k[j] = 4.0 * torch.sign(torch.randn(G, D, generator=g, dtype=F64))
+        v[j] = 10.0 * (1 + edge.index(j))
+    q[:, :, :] = q.abs() * torch.sign(k[edge[0]]).repeat_interleave(H // G, dim=0)      # queries lean towards edge keys
+    want = R.sink_attention(q, k.repeat_interleave(H // G, 1), v.repeat_interleave(H // G, 1), 0.4, 6.0, size or None)
+    nblk = (n + bs - 1) // bs
+    table = torch.randperm(nblk + 3, generator=g)[:nblk].tolist()
+    kc = torch.full((nblk + 3, G, bs, D), float("nan"), device=DEV)
+    vc = torch.full((nblk + 3, G, bs, Vd), float("nan"), device=DEV)
+    for j in range(n):
+        kc[table[j // bs], :, j % bs] = k[j].float().to(DEV)
+        vc[table[j // bs], :, j % bs] = v[j].float().to(DEV)
+    bt = _i32([table + [0] * 2])
+    qd = q.float().reshape(n, H * D).contiguous().to(DEV)
+    out = torch.zeros(n, H * Vd, device=DEV)
+    rc = lib.atx_attn_local(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), nblk + 2, _i32([0] * n).data_ptr(),
+                            _i32(list(range(n))).data_ptr(), None, 0, out.data_ptr(), H * Vd, n, H, G, D, Vd, bs, 0.4, 6.0,
+                            size, 1, 1.0, cabi.DT_F32, 0, _st())
+    assert rc == 0, lib.atx_last_error()
+    assert torch.allclose(out.cpu().double().view(n, H, Vd), want, atol=2e-4, rtol=2e-5)
+    one = torch.zeros(1, H * Vd, device=DEV)
+    for t in sorted(set(edge + [j + 1 for j in edge if j + 1 < n] + [n - 1])):
+        rc = lib.atx_attn_local(qd[t:t + 1].contiguous().data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), nblk + 2,
+                                _i32([0]).data_ptr(), _i32([t]).data_ptr(), None, 0, one.data_ptr(), H * Vd, 1, H, G, D, Vd,
+                                bs, 0.4, 6.0, size, 1, 1.0, cabi.DT_F32, 0, _st())
+        assert rc == 0
+        assert torch.allclose(one.cpu().double().view(H, Vd), want[t], atol=2e-4, rtol=2e-5), t
+
+
+@pytest.mark.parametrize("per_token", [False, True])
+def test_recurrence_remembers_a_far_key_across_steps_and_slots(per_token):
+    """One early token has a key and value far larger than the rest and the slowest head barely decays: hundreds of
+    tokens later the outputs are still made of it. The sequence is cut into steps of uneven sizes, beside a second
+    sequence in another slot, after the slots were filled with garbage."""
+    lib, cabi = _lib()
+    n, H, G, D, V = 700, 4, 2, 40, 24
+    g = torch.Generator().manual_seed(21)
+    q, k = torch.randn(n, G, D, generator=g, dtype=F64), torch.randn(n, G, D, generator=g, dtype=F64)
+    v = torch.randn(n, H, V, generator=g, dtype=F64)
+    k[3] *= 30.0
+    v[3] *= 30.0
+    q[-50:] = q[-50:].abs() * torch.sign(k[3])
+    qh, kh = q.repeat_interleave(H // G, 1), k.repeat_interleave(H // G, 1)
+    if per_token:
+        dt = 0.01 + 0.05 * torch.rand(n, H, generator=g, dtype=F64)
+        rate, skip = torch.tensor([0.01, 0.3, 2.0, 20.0], dtype=F64), torch.tensor([0.5, -1.0, 0.0, 2.0], dtype=F64)
+        want = R.selective_scan(v, kh, qh, dt, rate, skip)
+        dec_tok = torch.exp(-rate * dt).float().to(DEV).contiguous()
+        dt_d, skip_d = dt.float().to(DEV).contiguous(), skip.float().to(DEV)
+    else:
+        lam = torch.tensor([0.9995, 0.99, 0.9, 0.5], dtype=F64)
+        want = R.decayed_linear_attention(qh, kh, v, lam)
+        lam_d = lam.float().to(DEV)
+    assert want[-1].abs().max() > 50 * want[2].abs().max()          # the far token dominates the end
+    other = 17
+    qd = torch.cat([q, q[:other]]).float().reshape(-1, G * D).to(DEV)
+    state = torch.full((3, H, D, V), 1e30, device=DEV)
+    cuts, at, outs = [1, 2, 15, 16, 17, 33, 250, 1, 1, 300], 0, []
+    cuts.append(n - sum(cuts))
+    for i, c in enumerate(cuts):
+        with_other = i == 3                 # the other sequence runs whole beside the fourth portion, rows first
+        rows = list(range(at, at + c))
+        src = (list(range(other)) if with_other else []) + rows
+        idx = torch.tensor(src, device=DEV)
+        qs = q.float().reshape(n, G * D).to(DEV)[idx].contiguous()
+        ks = k.float().reshape(n, G * D).to(DEV)[idx].contiguous()
+        vs = v.float().reshape(n, H * V).to(DEV)[idx].contiguous()
+        y = torch.zeros(len(src), H * V, device=DEV)
+        seqs = ([(0, other, 0, 0)] if with_other else []) + [(len(src) - c, c, at, 2)]
+        a = [_i32([s[j] for s in seqs]) for j in range(4)]
+        if per_token:
+            rc = lib.atx_linear_recurrence(qs.data_ptr(), G * D, ks.data_ptr(), G * D, vs.data_ptr(), H * V, H, G, D, V, None,
+                                           dec_tok[idx].contiguous().data_ptr(), dt_d[idx].contiguous().data_ptr(),
+                                           skip_d.data_ptr(), 0, state.data_ptr(), y.data_ptr(), H * V, a[0].data_ptr(),
+                                           a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), len(seqs), 0, _st())
+        else:
+            rc = lib.atx_linear_recurrence(qs.data_ptr(), G * D, ks.data_ptr(), G * D, vs.data_ptr(), H * V, H, G, D, V,
+                                           lam_d.data_ptr(), None, None, None, 0, state.data_ptr(), y.data_ptr(), H * V,
+                                           a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), len(seqs), 0,
+                                           _st())
+        assert rc == 0, lib.atx_last_error()
+        if with_other:
+            assert torch.allclose(y[:other].cpu().double().view(other, H, V), want[:other], rtol=1e-4, atol=1e-3)
+        outs.append(y[len(src) - c:].cpu().double())
+        at += c
+    got = torch.cat(outs).view(n, H, V)
+    scale = want.abs().amax(dim=(1, 2), keepdim=True).clamp(min=1.0)
+    assert float(((got - want).abs() / scale).max()) < 2e-4
+
+
+def test_short_convolution_carries_its_window_across_short_steps():
+    lib, cabi = _lib()
+    n, Cc, H, K = 29, 37, 3, 4
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn(n, Cc + H + 5, generator=g, dtype=F64)           # [pad | channels | dt] in one row, pitch Cc + H + 5
+    taps, bias = torch.randn(Cc, K, generator=g, dtype=F64), torch.randn(Cc, generator=g, dtype=F64)
+    dt_bias, a_log = torch.randn(H, generator=g, dtype=F64), torch.randn(H, generator=g, dtype=F64)
+    want = R.swish(R.causal_taps(x[:, 5:5 + Cc], taps, bias))
+    want_dt = torch.log1p(torch.exp(x[:, 5 + Cc:] + dt_bias))
+    want_dec = torch.exp(-torch.exp(a_log) * want_dt)
+    xd = x.float().to(DEV).contiguous()
+    f = lambda t: t.float().to(DEV).contiguous()
+    taps_d, bias_d, dtb_d, al_d = f(taps), f(bias), f(dt_bias), f(a_log)
+    state = torch.full((2, K - 1, Cc), 1e30, device=DEV)
+    at, outs, dts, decs = 0, [], [], []
+    for c in [1, 1, 2, 1, 3, 5, 2, 14]:
+        rows = xd[at:at + c].contiguous()
+        out, dto, deco = torch.zeros(c, Cc, device=DEV), torch.zeros(c, H, device=DEV), torch.zeros(c, H, device=DEV)
+        s0, sc, sp, ss, ts = _i32([0]), _i32([c]), _i32([at]), _i32([1]), _i32([0] * c)
+        rc = lib.atx_conv_dt(rows.data_ptr(), Cc + H + 5, 5, 5 + Cc, taps_d.data_ptr(), bias_d.data_ptr(), dtb_d.data_ptr(),
+                             al_d.data_ptr(), state.data_ptr(), out.data_ptr(), dto.data_ptr(), deco.data_ptr(),
+                             ts.data_ptr(), s0.data_ptr(), sp.data_ptr(), ss.data_ptr(), c, Cc, H, K, cabi.DT_F32, 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        rc = lib.atx_conv_state_update(rows.data_ptr(), Cc + H + 5, 5, state.data_ptr(), s0.data_ptr(), sc.data_ptr(),
+                                       sp.data_ptr(), ss.data_ptr(), 1, Cc, K, 0, _st())
+        assert rc == 0
+        outs.append(out.cpu().double()), dts.append(dto.cpu().double()), decs.append(deco.cpu().double())
+        at += c
+    assert at == n
+    assert torch.allclose(torch.cat(outs), want, atol=1e-5)
+    assert torch.allclose(torch.cat(dts), want_dt, atol=1e-5) and torch.allclose(torch.cat(decs), want_dec, atol=1e-5)
+
+
+def test_fma_gemm_and_norm_kernels_match_their_formulas():
+    lib, cabi = _lib()
+    g = torch.Generator().manual_seed(41)
+    T, N, K = 37, 53, 75
+    for xt, dt, tol in ((torch.float32, cabi.DT_F32, 1e-5), (torch.bfloat16, cabi.DT_BF16, 1e-5)):
+        w = torch.randn(N, K, generator=g).to(xt).to(DEV)
+        x = torch.randn(T, K, generator=g).to(xt).to(DEV)
+        out = torch.zeros(T, N + 3, device=DEV)
+        rc = lib.atx_gemm_simple(w.data_ptr(), K, x.data_ptr(), K, out.data_ptr(), N + 3, T, N, K, 0, dt, 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        assert torch.allclose(out[:, :N].cpu().double(), x.cpu().double() @ w.cpu().double().T, atol=1e-4, rtol=tol)
+        assert float(out[:, N:].abs().max()) == 0.0
+    W = 70
+    h, y = torch.randn(T, W, generator=g, dtype=F64), 3.0 * torch.randn(T, W, generator=g, dtype=F64)
+    wp, vec, wn = (torch.randn(W, generator=g, dtype=F64) for _ in range(3))
+    hd, o = h.float().to(DEV), torch.zeros(T, W, device=DEV)
+    f = lambda t: t.float().to(DEV).contiguous()
+    rc = lib.atx_resid_norm(hd.data_ptr(), f(y).data_ptr(), f(wp).data_ptr(), f(vec).data_ptr(), f(wn).data_ptr(),
+                            o.data_ptr(), None, T, W, 1e-5, cabi.DT_F32, 0, _st())
+    assert rc == 0, lib.atx_last_error()
+    h2 = h + R.unit_rms(y, 1e-5) * wp + vec
+    assert torch.allclose(hd.cpu().double(), h2, atol=1e-5) and torch.allclose(o.cpu().double(), R.unit_rms(h2, 1e-5) * wn, atol=1e-5)
+    n, groups = 60, 3
+    yy, gg, ww = torch.randn(T, n, generator=g, dtype=F64), torch.randn(T, n, generator=g, dtype=F64), torch.randn(n, generator=g, dtype=F64)
+    for mode, want in ((0, R.unit_rms(yy, 1e-5) * ww * torch.sigmoid(gg) * 0.7),
+                       (1, R.unit_rms((yy * R.swish(gg)).view(T, groups, n // groups), 1e-5).reshape(T, n) * ww * 0.7)):
+        o = torch.zeros(T, n, device=DEV)
+        rc = lib.atx_gated_norm(f(yy).data_ptr(), n, f(gg).data_ptr(), n, f(ww).data_ptr(), o.data_ptr(), n, T, n,
+                                1 if mode == 0 else groups, 1e-5, mode, 0.7, cabi.DT_F32, 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        assert torch.allclose(o.cpu().double(), want, atol=1e-5), mode
