@@ -35,6 +35,7 @@ EXPORTS = [
     "atx_sample", "atx_sample_shard", "atx_sample_merge",
     "atx_gemm_simple", "atx_embed_rows", "atx_concat_embed", "atx_resid_norm", "atx_gated_act", "atx_gated_norm",
     "atx_conv_dt", "atx_conv_state_update", "atx_linear_recurrence", "atx_qk_prepare", "atx_attn_local",
+    "atx_attn_local_prefill", "atx_attn_local_prefill_supported",
 ]
 
 
@@ -98,7 +99,7 @@ def load() -> C.CDLL:
     lib.atx_gemm_simple.argtypes = [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, vp]
     lib.atx_embed_rows.argtypes = [vp, vp, vp, i32, i32, i32, i32, i32, vp]
     lib.atx_concat_embed.argtypes = [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp]
-    lib.atx_resid_norm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, i32, vp]
+    lib.atx_resid_norm.argtypes = [vp, vp, vp, vp, vp, vp, vp, i32, i32, f32, i32, vp, i64, i32, i32, vp]
     lib.atx_gated_act.argtypes = [vp, vp, i32, i32, i32, i32, vp]
     lib.atx_gated_norm.argtypes = [vp, i64, vp, i64, vp, vp, i64, i32, i32, i32, f32, i32, f32, i32, i32, vp]
     lib.atx_conv_dt.argtypes = [vp, i64, i32, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, i32, i32, i32,
@@ -110,6 +111,9 @@ def load() -> C.CDLL:
                                    i32, i32, i32, i32, f32, i32, i32, vp]
     lib.atx_attn_local.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, f32, f32,
                                    i32, i32, f32, i32, i32, vp]
+    lib.atx_attn_local_prefill_supported.argtypes = [i32, i32, i32]
+    lib.atx_attn_local_prefill.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, vp, i64, vp, i64, i32, i32, i32, i32,
+                                           i32, f32, f32, i32, i32, f32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

@@ -173,26 +173,27 @@ def _geometric_decays(heads: int) -> List[float]:
 
 def named_shape(name: str) -> Optional[Config]:
     """`random:safisun-<size>`: shapes whose layers resemble a real model's, for benchmarks (no checkpoint exists).
-    `safisun-8b` has the width, feed-forward size, head sizes and depth of the Llama 8B shape: 32 layer runs in the
-    pattern mamba2, mamba2, parallel (+ feed-forward), lightning (+ feed-forward)."""
+    `safisun-8b` / `safisun-1b` have the width, feed-forward size, head size, vocabulary and depth of the Llama 8B / 1B
+    shapes: layers in the pattern mamba2, mamba2, parallel, lightning, each with a feed-forward."""
     key = name.lower()
     shapes = {"safisun-8b": (4096, 14336, 8, 128256), "safisun-1b": (2048, 8192, 4, 128256),
-              "safisun-tiny": (256, 512, 1, 1024)}
+              "safisun-tiny": (256, 512, 1, 1024)}     # width, feed-forward, repeats of the 4-layer pattern, vocabulary
     if key not in shapes:
         return None
     W, F, groups, vocab = shapes[key]
     hd = 128 if W >= 4096 else 64
     heads = W // hd
-    mamba = {"type": "mamba2", "mlp": None,
+    ffn = {"ff": F, "kind": "dense"}
+    mamba = {"type": "mamba2", "mlp": ffn,
              "mixer": {"conv": 4, "groups": max(1, heads // 8), "heads": 2 * W // 64, "norm_groups": 1, "state": 128,
                        "vdim": 64}}
-    par = {"type": "parallel", "mlp": {"ff": F, "kind": "dense"},
+    par = {"type": "parallel", "mlp": ffn,
            "mixer": {"left": {"dim": hd, "heads": heads, "kv_heads": max(1, heads // 4), "mask": {"size": 2048},
                               "rot": {"base": 500000.0, "dims": hd // 2}, "scale": hd ** -0.5, "softcap": 50.0,
                               "vdim": hd},
                      "left_scale": 0.8, "right_scale": 1.1,
                      "right": {"decay": _geometric_decays(heads // 2), "dim": hd, "heads": heads // 2, "vdim": hd}}}
-    lin = {"type": "lightning", "mlp": {"ff": F, "kind": "dense"},
+    lin = {"type": "lightning", "mlp": ffn,
            "mixer": {"decay": _geometric_decays(heads), "dim": hd, "heads": heads, "vdim": hd}}
     layers = [mamba, mamba, par, lin] * groups
     cfg = Config(name=key, vocab_size=vocab, width=W, eps=1e-5, layers=[json.loads(json.dumps(l)) for l in layers],
@@ -357,9 +358,19 @@ class _Linear:
         assert x_buf.shape[1] == self.K and x_buf.is_contiguous() and w.is_contiguous()
         self.plan = _cabi.GemmPlan(w, x_buf) if _use_tc(w.dtype, self.K) else None
 
-    def run(self, out_ptr: int, ldo: int, T: int, flags: int, st: int, mode: int = _cabi.GEMM_STORE_F32) -> None:
+    def accumulates(self, T: int) -> bool:
+        """Decode-sized steps stream the weights once: the tcgen05 GEMM then cuts K over enough CTAs to fill the GPU
+        and ADDS its partial sums, so the target has to be zero before the launch."""
+        return self.plan is not None and T <= 64
+
+    def run(self, out_ptr: int, ldo: int, T: int, flags: int, st: int, mode: int = _cabi.GEMM_STORE_F32,
+            zeroed: bool = False) -> None:
         if self.plan is not None:
-            rc = self.lib.atx_gemm_run(self.plan._h, out_ptr, ldo, T, mode, 1, flags, st)
+            if zeroed and mode == _cabi.GEMM_STORE_F32 and self.accumulates(T):
+                rc = self.lib.atx_gemm_run(self.plan._h, out_ptr, ldo, T, _cabi.GEMM_ADD_F32, 0, flags, st)
+            else:
+                rc = self.lib.atx_gemm_run(self.plan._h, out_ptr, ldo, T, mode, 1 if mode == _cabi.GEMM_STORE_F32 else 0,
+                                           flags, st)
         else:
             assert mode == _cabi.GEMM_STORE_F32
             rc = self.lib.atx_gemm_simple(self.w.data_ptr(), self.K, self.x.data_ptr(), self.K, out_ptr, ldo, T, self.N,
@@ -417,7 +428,7 @@ class Program:
                 n_ff = max(n_ff, spec["mlp"]["ff"])
         self.h = torch.zeros(T, W, dtype=f32, device=dev)          # residual stream
         self.y = torch.zeros(T, W, dtype=f32, device=dev)          # a sublayer's output before its post-norm
-        self.proj = torch.zeros(T * n_in, dtype=f32, device=dev)   # every projection of the mixer input, fused
+        self.proj = torch.zeros(T * n_in + 4, dtype=f32, device=dev)   # every projection of the mixer input, fused
         self.rec = torch.zeros(T * n_rec, dtype=f32, device=dev)   # recurrence output
         self.xbc = torch.zeros(T * n_c, dtype=f32, device=dev)
         self.dtb = torch.zeros(2, T * n_h, dtype=f32, device=dev)  # step sizes, decays
@@ -508,9 +519,11 @@ class Program:
                               self.cfg.eps, 0, scale, self.dt, fl, st))
         return 2
 
-    def forward(self, T: int, n_seqs: int, n_rows: int) -> int:
-        """Issue every kernel of one step on the current stream; returns the launch count."""
+    def forward(self, T: int, n_dec: int, n_pf: int, n_rows: int) -> int:
+        """Issue every kernel of one step on the current stream; returns the launch count. The step's first n_dec
+        sequences are single decoded tokens (rows 0 .. n_dec-1), the next n_pf are prompt portions."""
         r, cfg, w = self.r, self.cfg, self.w
+        n_seqs = n_dec + n_pf
         lib, ck, dp, fl, dt = r.lib, r._ck, r._dp, r.flags, self.dt
         st = torch.cuda.current_stream().cuda_stream
         W, V, eps = cfg.width, cfg.vocab_size, cfg.eps
@@ -521,11 +534,15 @@ class Program:
         n += 1
         pending = None     # post-norm weight of the sublayer output waiting in y
         probe = r.layer_probe
+        small = T <= 64    # decode-sized: split-K GEMMs accumulate into buffers that the norm kernels hand back cleared
+        if small:
+            self.y[:T].zero_()
 
-        def resid(w_pre, out_ptr, vec=None, rows=None, rows_n: int = T) -> None:
+        def resid(w_pre, out_ptr, vec=None, rows=None, rows_n: int = T, zero_ptr=None, zero_bytes: int = 0) -> None:
             nonlocal n, pending
-            ck(lib.atx_resid_norm(h, y if pending is not None else None, pending, vec, w_pre, out_ptr, rows, rows_n, W,
-                                  eps, dt, fl, st))
+            have = pending is not None
+            ck(lib.atx_resid_norm(h, y if have else None, pending, vec, w_pre, out_ptr, rows, rows_n, W, eps,
+                                  1 if (have and rows is None and small) else 0, zero_ptr, zero_bytes, dt, fl, st))
             n += 1
             if rows is None:
                 pending = None
@@ -540,9 +557,11 @@ class Program:
                 self.lin_loop.run(h, W, T, fl, st)
                 n += 2
                 vec = w.loop_step.data_ptr() + p * W * self.esz
-            resid(l.norm1.data_ptr(), xn, vec=vec)
             ld = l.w_in.shape[0]
-            lin["in"].run(proj, ld, T, fl, st)
+            acc = lin["in"].accumulates(T)
+            resid(l.norm1.data_ptr(), xn, vec=vec, zero_ptr=proj if acc else None,
+                  zero_bytes=(T * ld * 4 + 15) // 16 * 16 if acc else 0)
+            lin["in"].run(proj, ld, T, fl, st, zeroed=acc)
             n += 1
             K_o = l.w_o.shape[1]
             mix = self.mix_flat.data_ptr()
@@ -579,13 +598,26 @@ class Program:
                                       l.q_norm.data_ptr(), l.k_norm.data_ptr(), table, rd, dp["pos"], dp["slots"], q,
                                       kc.data_ptr(), vc.data_ptr(), T, H, G, D, Vd, r.bs, eps, dt, fl, st))
                 chunk = int((a.get("mask") or {}).get("size", 0) or 0)
-                ck(lib.atx_attn_local(q, kc.data_ptr(), vc.data_ptr(), dp["seq_bt"], r.MB, dp["tok_seq"], dp["pos"],
-                                      proj + 4 * o_g, ld, mix, K_o, T, H, G, D, Vd, r.bs, float(a["scale"]),
-                                      float(a.get("softcap") or 0.0), chunk, 1, float(c["left_scale"]), dt, fl, st))
-                n += 2
+                # prompt portions on the tensor cores where the head sizes have such a kernel; single tokens (and every
+                # row otherwise) on the one-warp-per-row kernel
+                tc = n_pf > 0 and lib.atx_attn_local_prefill_supported(D, Vd, dt)
+                t_rows = n_dec if tc else T
+                args = (H, G, D, Vd, r.bs, float(a["scale"]), float(a.get("softcap") or 0.0), chunk, 1,
+                        float(c["left_scale"]), dt, fl, st)
+                if t_rows:
+                    ck(lib.atx_attn_local(q, kc.data_ptr(), vc.data_ptr(), dp["seq_bt"], r.MB, dp["tok_seq"], dp["pos"],
+                                          proj + 4 * o_g, ld, mix, K_o, t_rows, *args))
+                    n += 1
+                if tc:
+                    ck(lib.atx_attn_local_prefill(q, kc.data_ptr(), vc.data_ptr(), dp["seq_bt"] + 4 * n_dec * r.MB, r.MB,
+                                                  dp["seq_start"] + 4 * n_dec, dp["seq_count"] + 4 * n_dec,
+                                                  dp["seq_pos0"] + 4 * n_dec, n_pf, T - n_dec, proj + 4 * o_g, ld, mix,
+                                                  K_o, *args))
+                    n += 1
+                n += 1
                 n += self._lightning(l, b, proj, ld, o_right, self.state[ri], mix + H * Vd * self.esz, K_o,
                                      float(c["right_scale"]), T, n_seqs, fl, st)
-            lin["o"].run(y, W, T, fl, st)
+            lin["o"].run(y, W, T, fl, st, zeroed=small)
             n += 1
             pending = l.norm1b.data_ptr()
             if l.w_gu is not None:
@@ -599,7 +631,7 @@ class Program:
                     lin["gu"].run(self.gu.data_ptr(), 2 * F, T, fl, st)
                     ck(lib.atx_gated_act(self.gu.data_ptr(), act, T, F, dt, fl, st))
                     n += 2
-                lin["down"].run(y, W, T, fl, st)
+                lin["down"].run(y, W, T, fl, st, zeroed=small)
                 n += 1
                 pending = l.norm2b.data_ptr()
             if probe is not None:

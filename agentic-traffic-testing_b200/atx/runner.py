@@ -235,7 +235,7 @@ class ModelRunner:
         the same token on every rank, and the token the unsharded sampler draws. Only when a request asks for a
         nucleus (top_p < 1: `whole_rows`) are the rows themselves assembled (all-reduce of a zero-filled buffer)."""
         if self.program is not None:
-            return self.program.forward(T, n_dec + n_pf, n_rows)
+            return self.program.forward(T, n_dec, n_pf, n_rows)
         lib, m, w, ck = self.lib, self.m, self.w, self._ck
         st = torch.cuda.current_stream().cuda_stream
         fl = self.flags

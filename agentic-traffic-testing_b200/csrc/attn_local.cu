@@ -190,6 +190,237 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
     }
 }
 
+// ---- prompt portions on the tensor cores (bf16) -----------------------------------------------------------------------
+// One CTA = 64 consecutive rows of one sequence's portion x one query head; a warp owns 16 rows. Key tiles of 64
+// positions are gathered from the pages into shared memory; S = Q K^T and O += P V run on mma.sync m16n8k16 (bf16 in,
+// fp32 accumulate), everything between (scale, tanh cap, block-local causal mask, running maximum and sum with the
+// zero-score sink, rescale of O) is fp32 in registers. The portion's sequences are listed as (first row, rows, first
+// position); a CTA finds its tile by walking that list.
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+        "{%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float tanh_via_exp(float x) {
+    const float t = __expf(2.f * x);          // inf for large x: 2 / inf = 0 -> 1; 0 for very negative x -> -1
+    return 1.f - __fdividef(2.f, t + 1.f);
+}
+
+constexpr int kTcRows = 64, kTcKeys = 64;
+
+template <int D, int VD>
+__global__ void __launch_bounds__(128)
+attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
+                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
+                     const int* __restrict__ seq_start, const int* __restrict__ seq_count,
+                     const int* __restrict__ seq_pos0, int n_seqs, const float* __restrict__ gate, long long ldg,
+                     __nv_bfloat16* __restrict__ out, long long ldo, int H, int G, int bs, float scale, float softcap,
+                     int chunk, int sink, float out_scale) {
+    constexpr int LQ = D + 8, LV = VD + 8;     // padded rows: ldmatrix without bank conflicts, 16-byte aligned
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+    __nv_bfloat16* sK = sQ + kTcRows * LQ;
+    __nv_bfloat16* sV = sK + kTcKeys * LQ;
+    pdl_launch_dependents();
+    pdl_wait();
+    int tile = blockIdx.x, s = 0;
+    for (; s < n_seqs; ++s) {
+        const int nt = (seq_count[s] + kTcRows - 1) / kTcRows;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (s >= n_seqs) return;
+    const int h = blockIdx.y, g = h / (H / G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long row0 = seq_start[s] + tile * kTcRows;
+    const int nrows = min(kTcRows, seq_count[s] - tile * kTcRows);
+    const int p0 = seq_pos0[s] + tile * kTcRows, p1 = p0 + nrows - 1;
+    const int lo = chunk > 0 ? (p0 / chunk) * chunk : 0;
+    const int* bt = block_tables + static_cast<long long>(s) * max_blocks;
+
+    for (int c = threadIdx.x; c < kTcRows * (D / 8); c += 128) {
+        const int r = c / (D / 8), part = c - r * (D / 8);
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (r < nrows) v = __ldg(reinterpret_cast<const uint4*>(q + ((row0 + r) * H + h) * D + part * 8));
+        *reinterpret_cast<uint4*>(sQ + r * LQ + part * 8) = v;
+    }
+    __syncthreads();
+    uint32_t qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldsm_x4(smem_u32(sQ + (warp * 16 + (lane & 15)) * LQ + ks * 16 + (lane >> 4) * 8), qf[ks][0], qf[ks][1],
+                qf[ks][2], qf[ks][3]);
+    float o[VD / 8][4];
+#pragma unroll
+    for (int i = 0; i < VD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2], l[2];
+    m[0] = m[1] = sink ? 0.f : -INFINITY;     // the sink: a key of score 0 without a value
+    l[0] = l[1] = sink ? 1.f : 0.f;
+    int pr[2], plo[2];
+    pr[0] = p0 + warp * 16 + (lane >> 2);
+    pr[1] = pr[0] + 8;
+    plo[0] = chunk > 0 ? (pr[0] / chunk) * chunk : 0;
+    plo[1] = chunk > 0 ? (pr[1] / chunk) * chunk : 0;
+    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+
+    for (int k0 = lo; k0 <= p1; k0 += kTcKeys) {
+        __syncthreads();   // the previous tile has been consumed
+        for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
+            const int r = c / (D / 8), part = c - r * (D / 8);
+            const int kp = k0 + r;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (kp <= p1) {
+                const long long slot = (static_cast<long long>(bt[kp / bs]) * G + g) * bs + (kp % bs);
+                v = __ldg(reinterpret_cast<const uint4*>(k_cache + slot * D + part * 8));
+            }
+            *reinterpret_cast<uint4*>(sK + r * LQ + part * 8) = v;
+        }
+        for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
+            const int r = c / (VD / 8), part = c - r * (VD / 8);
+            const int kp = k0 + r;
+            uint4 v = make_uint4(0, 0, 0, 0);   // rows past the portion stay zero: 0 x garbage would not be 0
+            if (kp <= p1) {
+                const long long slot = (static_cast<long long>(bt[kp / bs]) * G + g) * bs + (kp % bs);
+                v = __ldg(reinterpret_cast<const uint4*>(v_cache + slot * VD + part * 8));
+            }
+            *reinterpret_cast<uint4*>(sV + r * LV + part * 8) = v;
+        }
+        __syncthreads();
+        if (k0 > p0 + warp * 16 + 15) continue;   // every key of the tile lies after this warp's rows (warp-uniform)
+        float sc[kTcKeys / 8][4];
+#pragma unroll
+        for (int i = 0; i < kTcKeys / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+#pragma unroll
+            for (int nb2 = 0; nb2 < kTcKeys / 16; ++nb2) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(sK + (nb2 * 16 + (lane >> 4) * 8 + (lane & 7)) * LQ + ks * 16 + ((lane >> 3) & 1) * 8), b0,
+                        b1, b2, b3);
+                mma_bf16(sc[2 * nb2], qf[ks], b0, b1);
+                mma_bf16(sc[2 * nb2 + 1], qf[ks], b2, b3);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int col = k0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                const int rr = e >> 1;
+                float v = sc[nb][e] * scale;
+                if (softcap > 0.f) v = softcap * tanh_via_exp(v * inv_cap);
+                if (col > pr[rr] || col < plo[rr]) v = -INFINITY;
+                sc[nb][e] = v;
+                mx[rr] = fmaxf(mx[rr], v);
+            }
+        }
+        float corr[2], rs[2] = {0.f, 0.f};
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
+            mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
+            const float mn = fmaxf(m[rr], mx[rr]);
+            corr[rr] = (m[rr] == -INFINITY) ? 0.f : __expf(m[rr] - mn);
+            m[rr] = mn;
+        }
+#pragma unroll
+        for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int rr = e >> 1;
+                const float p = (m[rr] == -INFINITY) ? 0.f : __expf(sc[nb][e] - m[rr]);
+                sc[nb][e] = p;
+                rs[rr] += p;
+            }
+        }
+#pragma unroll
+        for (int rr = 0; rr < 2; ++rr) {
+            rs[rr] += __shfl_xor_sync(0xffffffffu, rs[rr], 1);
+            rs[rr] += __shfl_xor_sync(0xffffffffu, rs[rr], 2);
+            l[rr] = l[rr] * corr[rr] + rs[rr];
+        }
+#pragma unroll
+        for (int i = 0; i < VD / 8; ++i) {
+            o[i][0] *= corr[0];
+            o[i][1] *= corr[0];
+            o[i][2] *= corr[1];
+            o[i][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < kTcKeys / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack_bf16(sc[2 * kk][0], sc[2 * kk][1]);
+            a[1] = pack_bf16(sc[2 * kk][2], sc[2 * kk][3]);
+            a[2] = pack_bf16(sc[2 * kk + 1][0], sc[2 * kk + 1][1]);
+            a[3] = pack_bf16(sc[2 * kk + 1][2], sc[2 * kk + 1][3]);
+#pragma unroll
+            for (int nb2 = 0; nb2 < VD / 16; ++nb2) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(smem_u32(sV + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LV + nb2 * 16 + (lane >> 4) * 8), b0,
+                          b1, b2, b3);
+                mma_bf16(o[2 * nb2], a, b0, b1);
+                mma_bf16(o[2 * nb2 + 1], a, b2, b3);
+            }
+        }
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int r = warp * 16 + (lane >> 2) + 8 * rr;
+        if (r >= nrows) continue;
+        float mul = out_scale / l[rr];
+        if (gate) mul *= 1.f / (1.f + __expf(-gate[(row0 + r) * ldg + h]));
+        __nv_bfloat16* orow = out + (row0 + r) * ldo + static_cast<long long>(h) * VD + (lane & 3) * 2;
+#pragma unroll
+        for (int nb = 0; nb < VD / 8; ++nb)
+            *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
+    }
+}
+
+template <int D, int VD>
+static int launch_attn_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                          int max_blocks, const int* seq_start, const int* seq_count, const int* seq_pos0, int n_seqs,
+                          int max_tiles, const float* gate, long long ldg, void* out, long long ldo, int H, int G, int bs,
+                          float scale, float softcap, int chunk, int sink, float out_scale, int flags,
+                          cudaStream_t stream) {
+    const int smem = (kTcRows + kTcKeys) * (D + 8) * 2 + kTcKeys * (VD + 8) * 2;
+    static bool attr_done = false;
+    if (!attr_done && smem > 48 * 1024) {
+        ATX_CUDA(cudaFuncSetAttribute(attn_local_tc_kernel<D, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(max_tiles, H);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    if (flags & ATX_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    using B = __nv_bfloat16;
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD>, reinterpret_cast<const B*>(q),
+                                reinterpret_cast<const B*>(k_cache), reinterpret_cast<const B*>(v_cache), block_tables,
+                                max_blocks, seq_start, seq_count, seq_pos0, n_seqs, gate, ldg, reinterpret_cast<B*>(out),
+                                ldo, H, G, bs, scale, softcap, chunk, sink, out_scale));
+    return ATX_OK;
+}
+
 }  // namespace atx
 
 using namespace atx;
@@ -278,6 +509,36 @@ int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, cons
                                     Vd, block_size, scale, softcap, chunk, sink, out_scale));
     }
     return ATX_OK;
+}
+
+int atx_attn_local_prefill_supported(int D, int Vd, int dtype) {
+    return dtype == ATX_DT_BF16 && ((D == 64 && Vd == 64) || (D == 128 && Vd == 128)) ? 1 : 0;
+}
+
+int atx_attn_local_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                           int max_blocks, const int* seq_start, const int* seq_count, const int* seq_pos0, int n_seqs,
+                           int total_rows, const float* gate, long long ldg, void* out, long long ldo, int H, int G, int D,
+                           int Vd, int block_size, float scale, float softcap, int chunk, int sink, float out_scale,
+                           int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && seq_start && seq_count && seq_pos0 && out,
+                "atx_attn_local_prefill: null pointer");
+    ATX_REQUIRE(n_seqs > 0 && total_rows > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0,
+                "atx_attn_local_prefill: bad shape n_seqs=%d rows=%d H=%d G=%d", n_seqs, total_rows, H, G);
+    if (!atx_attn_local_prefill_supported(D, Vd, dtype)) {
+        set_error("atx_attn_local_prefill: bf16 with head sizes (64, 64) or (128, 128) only; got D=%d Vd=%d dtype=%d", D, Vd,
+                  dtype);
+        return ATX_ERR_UNSUPPORTED;
+    }
+    // every sequence adds at most one partly filled tile
+    const int max_tiles = (total_rows + kTcRows - 1) / kTcRows + n_seqs;
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    if (D == 64)
+        return launch_attn_tc<64, 64>(q, k_cache, v_cache, block_tables, max_blocks, seq_start, seq_count, seq_pos0, n_seqs,
+                                      max_tiles, gate, ldg, out, ldo, H, G, block_size, scale, softcap, chunk, sink,
+                                      out_scale, flags, st);
+    return launch_attn_tc<128, 128>(q, k_cache, v_cache, block_tables, max_blocks, seq_start, seq_count, seq_pos0, n_seqs,
+                                    max_tiles, gate, ldg, out, ldo, H, G, block_size, scale, softcap, chunk, sink,
+                                    out_scale, flags, st);
 }
 
 }  // extern "C"

@@ -86,15 +86,25 @@ __global__ void __launch_bounds__(128) concat_embed_kernel(const float* __restri
 // ---- residual update between two norms ---------------------------------------------------------------------------
 // h[r] += rms(y[r]) * w_post (if y) + vec (if vec);  out[t] = rms(h[r]) * w_pre (if w_pre);  r = rows ? rows[t] : t.
 // With `rows` the residual itself is left untouched (the gathered rows feed the LM head only).
+// zero_y: the row of y is cleared once it has been read, so that the next split-K GEMM can accumulate into it;
+// CTAs beyond T clear zero_ptr (the accumulator of the GEMM that consumes `out`).
 template <typename XT>
 __global__ void __launch_bounds__(256)
-resid_norm_kernel(float* __restrict__ h, const float* __restrict__ y, const XT* __restrict__ w_post,
+resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __restrict__ w_post,
                   const XT* __restrict__ vec, const XT* __restrict__ w_pre, XT* __restrict__ out,
-                  const int* __restrict__ rows, int W, float eps) {
+                  const int* __restrict__ rows, int T, int W, float eps, int zero_y, uint4* __restrict__ zero_ptr,
+                  long long zero_vecs) {
     extern __shared__ float srow[];
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
+    if (blockIdx.x >= T) {
+        const long long nb = gridDim.x - T;
+        for (long long i = static_cast<long long>(blockIdx.x - T) * blockDim.x + threadIdx.x; i < zero_vecs;
+             i += nb * blockDim.x)
+            zero_ptr[i] = make_uint4(0, 0, 0, 0);
+        return;
+    }
     const int t = blockIdx.x;
     const long long r = rows ? rows[t] : t;
     float* hr = h + r * W;
@@ -103,6 +113,7 @@ resid_norm_kernel(float* __restrict__ h, const float* __restrict__ y, const XT* 
         float ss = 0.f;
         for (int i = threadIdx.x; i < W; i += blockDim.x) {
             const float v = y[r * W + i];
+            if (zero_y) y[r * W + i] = 0.f;
             srow[i] = v;
             ss += v * v;
         }
@@ -390,15 +401,22 @@ int atx_concat_embed(const float* h, const int* ids, const void* table, void* ou
     return ATX_OK;
 }
 
-int atx_resid_norm(float* h, const float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
-                   const int* rows, int T, int W, float eps, int dtype, int flags, atx_stream_t stream) {
+int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
+                   const int* rows, int T, int W, float eps, int zero_y, void* zero_ptr, long long zero_bytes, int dtype,
+                   int flags, atx_stream_t stream) {
     ATX_REQUIRE(h, "atx_resid_norm: null pointer");
     ATX_REQUIRE(T > 0 && W > 0 && W <= 12288, "atx_resid_norm: bad shape T=%d W=%d (W <= 12288)", T, W);
     ATX_REQUIRE((y == nullptr) == (w_post == nullptr), "atx_resid_norm: y and w_post come together");
     ATX_REQUIRE((w_pre == nullptr) == (out == nullptr), "atx_resid_norm: w_pre and out come together");
+    ATX_REQUIRE(zero_bytes >= 0 && zero_bytes % 16 == 0 && (zero_bytes == 0 || zero_ptr) && !(zero_y && rows),
+                "atx_resid_norm: zero_bytes=%lld must be a non-negative multiple of 16 with a buffer; zero_y not with rows",
+                zero_bytes);
+    const long long zv = zero_bytes / 16;
+    long long zb = (zv + 256 * 8 - 1) / (256 * 8);
+    if (zb > 2048) zb = 2048;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    cfg.gridDim = dim3(T);
+    cfg.gridDim = dim3(static_cast<unsigned>(T + zb));
     cfg.blockDim = dim3(256);
     cfg.dynamicSmemBytes = static_cast<size_t>(W) * 4;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
@@ -406,7 +424,8 @@ int atx_resid_norm(float* h, const float* y, const void* w_post, const void* vec
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
                                &cfg, resid_norm_kernel<XT>, h, y, reinterpret_cast<const XT*>(w_post),
                                reinterpret_cast<const XT*>(vec), reinterpret_cast<const XT*>(w_pre),
-                               reinterpret_cast<XT*>(out), rows, W, eps)));
+                               reinterpret_cast<XT*>(out), rows, T, W, eps, zero_y, reinterpret_cast<uint4*>(zero_ptr),
+                               zv)));
     return ATX_OK;
 }
 

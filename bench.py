@@ -514,6 +514,77 @@ def routed_trace_measure(world: int, device_ecfg, model: str = "random:8b:0") ->
 
 
 # ------------------------------------------------------------------------------------------------------
+def safisun_measure(args, local, pk) -> dict:
+    """`--workload safisun`: prefill and decode throughput of the Safisun family (state-space, linear-attention and
+    block-local attention mixers) at shapes with the width, depth, feed-forward size and vocabulary of Llama shapes,
+    each beside that Llama shape through the same engine: B prompts of P random tokens (chunked prefill, 8192-token
+    budget) + O greedy tokens, random-init weights, prefix cache off. Steps are timed on the device with CUDA events
+    (the runner's step_events); weights (>= 2.5 GB) exceed L2, so every step streams them from HBM."""
+    import gc
+
+    import numpy as np
+    import torch
+
+    from atx.config import EngineConfig, resolve_model
+    from atx.engine import LLMEngine
+    from atx.scheduler import SamplingParams
+
+    B, P, O = args.arch_batch, args.arch_prompt, args.arch_out
+    records, launches = [], 0
+    for size in [x for x in args.arch_sizes.split(",") if x]:
+        for model in (f"random:safisun-{size}:0", f"random:{size}:0"):
+            src = resolve_model(model)
+            ecfg = EngineConfig(max_model_len=P + O + 16, max_num_seqs=B, max_num_batched_tokens=8192,
+                                gpu_memory_utilization=0.5, enable_prefix_caching=False, device=local)
+            engine = LLMEngine(src, ecfg)
+            r, mcfg = engine.runner, src.config
+
+            def one(step):
+                rng = np.random.default_rng(11 + step)
+                prompts = [rng.integers(0, mcfg.vocab_size - 1, P).tolist() for _ in range(B)]
+                params = SamplingParams(temperature=0.0, max_tokens=O, ignore_eos=True)
+                r.step_events = []
+                for i, p in enumerate(prompts):
+                    engine.add_request(f"a{step}-{i}", p, params)
+                while engine.has_work():
+                    engine.step()
+                torch.cuda.synchronize()
+                ev, r.step_events = r.step_events, None
+                return ev
+            for w in range(args.warmup):
+                one(1000 + w)
+            evs = []
+            for k in range(args.steps):
+                evs += one(k)
+            dec = [a.elapsed_time(b) for (a, b, nd, npf, ctx) in evs if npf == 0 and nd == B]
+            pf = [(a.elapsed_time(b), npf) for (a, b, nd, npf, ctx) in evs if npf > 0]
+            ms = statistics.median(dec)
+            pf_ms, pf_tok = sum(x[0] for x in pf), sum(x[1] for x in pf)
+            wbytes = mcfg.weight_bytes_per_decode_step()
+            state = getattr(mcfg, "state_bytes_per_sequence", lambda: 0)()
+            byts = wbytes + 2 * state * B + mcfg.kv_bytes_per_token() * B * (P + O // 2) * (0 if state else 1)
+            records.append({"model": model, "params_bytes": wbytes, "layers": mcfg.num_hidden_layers,
+                            "prefill_tokens_per_s": round(pf_tok / pf_ms * 1e3), "prefill_ms_per_8192_tokens":
+                            round(pf_ms / pf_tok * 8192, 2),
+                            "prefill_tflops_weights_only": round(wbytes * pf_tok / pf_ms / 1e9, 1),   # 2 FLOP per weight
+                            "decode_ms_per_step": round(ms, 3), "decode_tokens_per_s": round(B / ms * 1e3, 1),
+                            "decode_algorithmic_bytes": round(byts), "decode_gbs": round(byts / ms / 1e6, 1),
+                            "decode_frac_of_measured_hbm_peak": round(byts / ms / 1e6 / pk["hbm_gbs"], 4),
+                            "launches_per_decode_step": r.launches_last_step, "state_bytes_per_sequence": state})
+            launches += r.kernel_launches
+            r.close()
+            del engine, r
+            gc.collect()
+            torch.cuda.empty_cache()
+    mine = [x for x in records if "safisun" in x["model"]]
+    return {"metric": "Safisun decode tokens/s beside Llama at equal width, depth, feed-forward and vocabulary",
+            "value": mine[-1]["decode_tokens_per_s"], "ms_per_step": mine[-1]["decode_ms_per_step"], "scaling": "weak",
+            "records": records, "gpu_launches": launches, "peak": pk,
+            "config": {"workload": f"batch {B} x {P}-token random prompts (chunked prefill, 8192-token budget) + {O} "
+                                   "greedy tokens; random-init weights; prefix cache off; inputs larger than L2",
+                       "parallelism": "1 GPU", "global_batch": B, "seq_len": P}}
+
+
 def run_other_workload(args, rank, world, local):
     """BASELINE.json configs[2..4]: opt-in workloads (`--workload trace|long|tp70b`). Each prints one JSON
     line of the same shape as the headline run (value = aggregate output tokens/s)."""
@@ -626,6 +697,13 @@ def run_other_workload(args, rank, world, local):
                     "config": {"workload": f"BASELINE configs[4]: Llama-3.1-8B long-context, batch {B} x {P}-token prompts "
                                            f"(chunked prefill, 8192-token budget) + {O} greedy tokens over paged KV",
                                "parallelism": "1 GPU", "kv_blocks": r.num_blocks}})
+    elif args.workload == "safisun":
+        out.update(safisun_measure(args, local, pk))
+        if rank == 0:
+            print(json.dumps(out), flush=True)
+        if dist is not None:
+            dist.destroy_process_group()
+        return
     elif args.workload == "tp70b":
         out.update(tp70b_measure(dist, rank, world, local, pk, args.steps, args.warmup, args.tp_out, args.layers))
         if rank == 0:
@@ -654,7 +732,12 @@ def main() -> None:
     ap.add_argument("--no-multi", action="store_true", help="N > 1: skip the routed-DP and 70B-TP records")
     ap.add_argument("--tp70b-any-n", action="store_true", help="attach the 70B tensor-parallel record at any N > 1 "
                                                                "(default: only at N = 8, BASELINE configs[3])")
-    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b"],
+    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun: shapes to run (each beside the Llama shape "
+                                                          "of the same width, depth, feed-forward and vocabulary)")
+    ap.add_argument("--arch-batch", type=int, default=8)
+    ap.add_argument("--arch-prompt", type=int, default=2048)
+    ap.add_argument("--arch-out", type=int, default=64)
+    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun"],
                     help="fanout = headline BASELINE configs[1] (default); the others are configs[2..4]")
     ap.add_argument("--trace-out", default="", help="directory for response.json / llm_calls.jsonl of a trace replay")
     ap.add_argument("--long-out", type=int, default=128)

@@ -231,9 +231,12 @@ int atx_concat_embed(const float* h, const int* ids, const void* table, void* ou
                      int flags, atx_stream_t stream);
 /* Residual update between two RMS norms, one pass over the row:
  *   h[r] += rms(y[r]) * w_post  (if y)  + vec (if vec);   out[t] = rms(h[r]) * w_pre  (if w_pre);   r = rows ? rows[t] : t
- * rms(x) = x / sqrt(mean(x^2) + eps). With `rows` the residual is read only. */
-int atx_resid_norm(float* h, const float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
-                   const int* rows, int T, int W, float eps, int dtype, int flags, atx_stream_t stream);
+ * rms(x) = x / sqrt(mean(x^2) + eps). With `rows` the residual is read only. zero_y != 0 clears each row of y once it
+ * has been read, and spare CTAs clear zero_ptr / zero_bytes (a multiple of 16): the accumulators of the split-K GEMMs
+ * that run next. */
+int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, const void* w_pre, void* out,
+                   const int* rows, int T, int W, float eps, int zero_y, void* zero_ptr, long long zero_bytes, int dtype,
+                   int flags, atx_stream_t stream);
 /* out[t, i] = silu(gu[t, i]) * gu[t, I + i] */
 int atx_gated_act(const float* gu, void* out, int T, int I, int dtype, int flags, atx_stream_t stream);
 /* Gated RMS norm over n / groups consecutive elements at a time:
@@ -276,6 +279,16 @@ int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, cons
                    const int* tok_seq, const int* positions, const float* gate, long long ldg, void* out, long long ldo,
                    int T, int H, int G, int D, int Vd, int block_size, float scale, float softcap, int chunk, int sink,
                    float out_scale, int dtype, int flags, atx_stream_t stream);
+/* The same attention for prompt portions on the tensor cores (mma.sync m16n8k16, bf16 operands, fp32 softmax and
+ * accumulation): sequences are given as (first row, rows, first position) triples, block_tables has one row per listed
+ * sequence. ..._supported() says whether the head sizes and element type have a tensor-core kernel (else use
+ * atx_attn_local for those rows too). total_rows bounds the sum of the sequences' rows. */
+int atx_attn_local_prefill_supported(int D, int Vd, int dtype);
+int atx_attn_local_prefill(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
+                           int max_blocks, const int* seq_start, const int* seq_count, const int* seq_pos0, int n_seqs,
+                           int total_rows, const float* gate, long long ldg, void* out, long long ldo, int H, int G, int D,
+                           int Vd, int block_size, float scale, float softcap, int chunk, int sink, float out_scale,
+                           int dtype, int flags, atx_stream_t stream);
 
 #ifdef __cplusplus
 }

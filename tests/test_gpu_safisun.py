@@ -87,20 +87,27 @@ def whole(eng, rid, toks, end=True):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("width", [64, 96])       # 96: not a multiple of the tensor-core GEMM's K block
-@pytest.mark.parametrize("kind", ["lightning", "mamba2", "parallel", "parallel_full", "lightning_ffn"])
+@pytest.mark.parametrize("kind", ["lightning", "mamba2", "parallel", "parallel_full", "parallel_tc", "lightning_ffn"])
 def test_one_layer_models(kind, width, dtype):
     layer = {"lightning": lightning_layer(), "mamba2": mamba_layer(),
              "parallel": parallel_layer(), "parallel_full": parallel_layer(size=None, rot_dims=16, kv=4),
+             "parallel_tc": parallel_layer(size=24, rot_dims=32, dim=64, vdim=64, heads=4, kv=2),   # tensor-core head sizes
              "lightning_ffn": lightning_layer(heads=1, dim=4, vdim=4, decay=[0.9], mlp={"ff": 24, "kind": "dense"})}[kind]
     if kind == "parallel_full":
         layer["mixer"]["left"]["mask"] = None
         layer["mixer"]["left"]["softcap"] = None
     cfg = model_cfg([layer], width=width)
     wt = R.random_checkpoint(cfg, 11)
-    toks = tokens(45, seed=1)
+    toks = tokens(150 if kind == "parallel_tc" else 45, seed=1)
     eng = engine(cfg, wt, dtype)
     got = whole(eng, "a", toks)
-    assert rel(got, R.forward(cfg, wt, toks)) < TOL[dtype]
+    want = R.forward(cfg, wt, toks)
+    assert rel(got, want) < TOL[dtype]
+    if kind == "parallel_tc":      # portions that start inside a block and inside a 64-row tile, beside a decoded token
+        a = eng.feed([("p", toks[:70], list(range(70)))], [])
+        b = eng.feed([("p", toks[70:71], [0]), ("q", toks[:131], list(range(131)))], ["q"])
+        c = eng.feed([("p", toks[71:], list(range(79)))], ["p"])
+        assert rel(np.concatenate([a, b[:1], c]), want) < TOL[dtype] and rel(b[1:], want[:131]) < TOL[dtype]
 
 
 def test_first_tokens_of_a_sequence():
@@ -297,6 +304,51 @@ def test_attention_block_edges_with_dominant_keys(size, n):
         assert torch.allclose(one.cpu().double().view(H, Vd), want[t], atol=2e-4, rtol=2e-5), t
 
 
+@pytest.mark.parametrize("D,size,pos0,n", [(64, 24, 0, 200), (64, 64, 37, 150), (128, 0, 5, 130), (128, 100, 99, 234)])
+def test_tensor_core_attention_block_edges_with_dominant_keys(D, size, pos0, n):
+    """The prompt-portion kernel on bf16 pages: positions pos0 .. pos0+n-1 are this step's rows (earlier keys are in
+    the pages already), block edges carry dominant keys with values of their own, a second short sequence shares the
+    launch. Every input is exactly representable in bf16; the probabilities are rounded to bf16 inside the kernel."""
+    lib, cabi = _lib()
+    H, G, bs, total = 4, 2, 16, pos0 + n
+    g = torch.Generator().manual_seed(D + size + n)
+    bf = lambda t: t.to(torch.bfloat16).to(F64)
+    q = bf(torch.randn(total, H, D, generator=g, dtype=F64))
+    k = bf(0.1 * torch.randn(total, G, D, generator=g, dtype=F64))
+    v = bf(torch.randn(total, G, D, generator=g, dtype=F64))
+    edge = sorted({j for j in range(total) if size and (j % size in (0, size - 1))} | {pos0, max(0, pos0 - 1), 63, 64, 127, 128} & set(range(total)))
+    for i, j in enumerate(edge):
+        k[j] = bf(0.5 * torch.sign(torch.randn(G, D, generator=g, dtype=F64)))
+        v[j] = float(8 * (1 + i % 30))
+    q = bf(q.abs() * torch.sign(k[edge[0]]).repeat_interleave(H // G, dim=0))
+    want = R.sink_attention(q, k.repeat_interleave(H // G, 1), v.repeat_interleave(H // G, 1), 0.3, 7.0, size or None)
+    nblk = (total + bs - 1) // bs
+    table = torch.randperm(nblk + 5, generator=g)[:nblk].tolist()
+    kc = torch.full((nblk + 5, G, bs, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    vc = torch.full((nblk + 5, G, bs, D), float("nan"), device=DEV, dtype=torch.bfloat16)
+    for j in range(total):
+        kc[table[j // bs], :, j % bs] = k[j].to(torch.bfloat16).to(DEV)
+        vc[table[j // bs], :, j % bs] = v[j].to(torch.bfloat16).to(DEV)
+    short = min(9, total)                                   # a second sequence: the first `short` positions, rows first
+    bt = _i32([table + [0] * 4, table + [0] * 4])
+    rows = list(range(short)) + list(range(pos0, total))
+    qd = q[rows].to(torch.bfloat16).reshape(len(rows), H * D).contiguous().to(DEV)
+    gate = torch.randn(len(rows), H, generator=g).to(DEV).contiguous()
+    out = torch.zeros(len(rows), H * D + 8, device=DEV, dtype=torch.bfloat16)
+    s0, sc, sp = _i32([0, short]), _i32([short, n]), _i32([0, pos0])
+    assert lib.atx_attn_local_prefill_supported(D, D, cabi.DT_BF16) == 1
+    rc = lib.atx_attn_local_prefill(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), nblk + 4, s0.data_ptr(),
+                                    sc.data_ptr(), sp.data_ptr(), 2, len(rows), gate.data_ptr(), H, out.data_ptr(), H * D + 8,
+                                    H, G, D, D, bs, 0.3, 7.0, size, 1, 0.5, cabi.DT_BF16, 0, _st())
+    assert rc == 0, lib.atx_last_error()
+    torch.cuda.synchronize()
+    got = out[:, :H * D].float().cpu().double().view(len(rows), H, D)
+    ref = want[rows] * torch.sigmoid(gate.cpu().double())[:, :, None] * 0.5
+    assert float(out[:, H * D:].float().abs().max()) == 0.0
+    scale = ref.abs().amax(dim=(1, 2), keepdim=True).clamp(min=1.0)
+    assert float(((got - ref).abs() / scale).max()) < 2e-2
+
+
 @pytest.mark.parametrize("per_token", [False, True])
 def test_recurrence_remembers_a_far_key_across_steps_and_slots(per_token):
     """One early token has a key and value far larger than the rest and the slowest head barely decays: hundreds of
@@ -412,9 +464,10 @@ def test_fma_gemm_and_norm_kernels_match_their_formulas():
     f = lambda t: t.float().to(DEV).contiguous()
     yd, wpd, vecd, wnd = f(y), f(wp), f(vec), f(wn)
     rc = lib.atx_resid_norm(hd.data_ptr(), yd.data_ptr(), wpd.data_ptr(), vecd.data_ptr(), wnd.data_ptr(),
-                            o.data_ptr(), None, T, W, 1e-5, cabi.DT_F32, 0, _st())
+                            o.data_ptr(), None, T, W, 1e-5, 1, None, 0, cabi.DT_F32, 0, _st())
     assert rc == 0, lib.atx_last_error()
     h2 = h + R.unit_rms(y, 1e-5) * wp + vec
+    assert float(yd.abs().max()) == 0.0        # the sublayer output is handed back cleared
     assert torch.allclose(hd.cpu().double(), h2, atol=1e-5) and torch.allclose(o.cpu().double(), R.unit_rms(h2, 1e-5) * wn, atol=1e-5)
     n, groups = 60, 3
     yy, gg, ww = torch.randn(T, n, generator=g, dtype=F64), torch.randn(T, n, generator=g, dtype=F64), torch.randn(n, generator=g, dtype=F64)
