@@ -89,7 +89,7 @@ __global__ void __launch_bounds__(128) concat_embed_kernel(const float* __restri
 // zero_y: the row of y is cleared once it has been read, so that the next split-K GEMM can accumulate into it;
 // CTAs beyond T clear zero_ptr (the accumulator of the GEMM that consumes `out`).
 template <typename XT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __restrict__ w_post,
                   const XT* __restrict__ vec, const XT* __restrict__ w_pre, XT* __restrict__ out,
                   const int* __restrict__ rows, int T, int W, float eps, int zero_y, uint4* __restrict__ zero_ptr,
@@ -154,7 +154,7 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
 // mode 1: u = y * silu(g); out = rms(u) * w * scale  (gate before the norm)
 // The norm runs over n / groups consecutive elements; grid (T, groups).
 template <typename XT>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ gate, long long ldg,
                   const XT* __restrict__ w, XT* __restrict__ out, long long ldo, int n_group, float eps, int mode,
                   float scale) {
@@ -203,7 +203,7 @@ conv_dt_kernel(const float* __restrict__ in, long long ld, int x_off, int dt_off
     const int i = static_cast<int>(t) - seq_start[s];
     const int pos0 = seq_pos0[s];
     const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
-    for (int c = threadIdx.x; c < C + H; c += blockDim.x) {
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < C + H; c += gridDim.y * blockDim.x) {
         if (c < C) {
             float acc = ldf(b, c);
             for (int j = 0; j < K; ++j) {
@@ -261,9 +261,9 @@ conv_state_update_kernel(const float* __restrict__ in, long long ld, int x_off, 
 // One CTA owns a V-tile of one head of one sequence and walks the sequence's rows in order. A thread keeps DS rows of
 // one column of S in registers for the whole walk (the state is read once and written once per step); rows are staged
 // through shared memory kChunk at a time, and the partial dot products of the D-slices are summed per chunk.
-constexpr int kRecChunk = 16;
+constexpr int kRecChunk = 32;
 
-template <int DS>
+template <int DS, bool FULL>   // FULL: D is a multiple of DS (no partial slice) and rows of q / k are 16-byte aligned
 __global__ void __launch_bounds__(256)
 linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
                          const float* __restrict__ v, long long ldv, int H, int G, int D, int V,
@@ -272,7 +272,7 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
                          float* __restrict__ state, float* __restrict__ y, long long ldy,
                          const int* __restrict__ seq_start, const int* __restrict__ seq_count,
                          const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int VT, int DG) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     pdl_launch_dependents();
     pdl_wait();
     const int s = blockIdx.x, h = blockIdx.y;
@@ -326,11 +326,28 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
                 const float* qi = sq + i * D + d0;
                 const float* ki = sk + i * D + d0;
                 float acc = 0.f;
+                if (FULL) {
+                    const float4* q4 = reinterpret_cast<const float4*>(qi);
+                    const float4* k4 = reinterpret_cast<const float4*>(ki);
 #pragma unroll
-                for (int d = 0; d < DS; ++d) {
-                    if (d0 + d < D) {
-                        S[d] = fmaf(a, S[d], ki[d] * vv);
-                        acc = fmaf(S[d], qi[d], acc);
+                    for (int d = 0; d < DS / 4; ++d) {
+                        const float4 kk = k4[d], qq = q4[d];
+                        S[4 * d] = fmaf(a, S[4 * d], kk.x * vv);
+                        S[4 * d + 1] = fmaf(a, S[4 * d + 1], kk.y * vv);
+                        S[4 * d + 2] = fmaf(a, S[4 * d + 2], kk.z * vv);
+                        S[4 * d + 3] = fmaf(a, S[4 * d + 3], kk.w * vv);
+                        acc = fmaf(S[4 * d], qq.x, acc);
+                        acc = fmaf(S[4 * d + 1], qq.y, acc);
+                        acc = fmaf(S[4 * d + 2], qq.z, acc);
+                        acc = fmaf(S[4 * d + 3], qq.w, acc);
+                    }
+                } else {
+#pragma unroll
+                    for (int d = 0; d < DS; ++d) {
+                        if (d0 + d < D) {
+                            S[d] = fmaf(a, S[d], ki[d] * vv);
+                            acc = fmaf(S[d], qi[d], acc);
+                        }
                     }
                 }
                 sp[(i * DG + dg) * VT + tv] = acc;
@@ -417,7 +434,7 @@ int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, cons
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(static_cast<unsigned>(T + zb));
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(T <= 512 && W >= 2048 ? 1024 : 256);   // few rows: more warps per row hide the load latency
     cfg.dynamicSmemBytes = static_cast<size_t>(W) * 4;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
@@ -455,7 +472,7 @@ int atx_gated_norm(const float* y, long long ldy, const float* gate, long long l
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(T, groups);
-    cfg.blockDim = dim3(256);
+    cfg.blockDim = dim3(T <= 512 && n / groups >= 2048 ? 1024 : 256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_kernel<XT>, y, ldy, gate, ldg,
@@ -474,7 +491,8 @@ int atx_conv_dt(const float* in, long long ld, int x_off, int dt_off, const void
     ATX_REQUIRE(T > 0 && C > 0 && H > 0 && K >= 1, "atx_conv_dt: bad shape T=%d C=%d H=%d K=%d", T, C, H, K);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    cfg.gridDim = dim3(T);
+    // few rows (decode): spread a row's channels over several CTAs
+    cfg.gridDim = dim3(T, T >= 256 ? 1 : (C + H + 255) / 256);
     cfg.blockDim = dim3(256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
@@ -530,21 +548,25 @@ int atx_linear_recurrence(const float* q, long long ldq, const float* k, long lo
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
     ATX_REQUIRE(smem <= 160 * 1024, "atx_linear_recurrence: D=%d needs %zu bytes of shared memory", D, smem);
-    if (DS == 32) {
-        if (smem > 48 * 1024)
-            ATX_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-        ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<32>, q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head,
-                                    decay_tok, kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0,
-                                    seq_slot, VT, DG));
-    } else {
-        if (smem > 48 * 1024)
-            ATX_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                          static_cast<int>(smem)));
-        ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<64>, q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head,
-                                    decay_tok, kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0,
-                                    seq_slot, VT, DG));
-    }
+    const bool full = D % DS == 0 && D % 4 == 0;
+#define ATX_REC_LAUNCH(DS_, FULL_)                                                                                       \
+    do {                                                                                                                  \
+        if (smem > 48 * 1024)                                                                                             \
+            ATX_CUDA(cudaFuncSetAttribute(linear_recurrence_kernel<DS_, FULL_>,                                           \
+                                          cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)));          \
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, linear_recurrence_kernel<DS_, FULL_>, q, ldq, k, ldk, v, ldv, H, G, D, V,       \
+                                    decay_head, decay_tok, kscale_tok, skip, act, state, y, ldy, seq_start, seq_count,   \
+                                    seq_pos0, seq_slot, VT, DG));                                                         \
+    } while (0)
+    if (DS == 32 && full)
+        ATX_REC_LAUNCH(32, true);
+    else if (DS == 32)
+        ATX_REC_LAUNCH(32, false);
+    else if (full)
+        ATX_REC_LAUNCH(64, true);
+    else
+        ATX_REC_LAUNCH(64, false);
+#undef ATX_REC_LAUNCH
     return ATX_OK;
 }
 
