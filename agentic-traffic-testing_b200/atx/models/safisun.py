@@ -47,6 +47,7 @@ class Config:
     loop: Optional[dict] = None                        # {"start", "stop", "times"}
     eos_token_ids: tuple = ()
     bos_token_id: int = 0
+    max_position_embeddings: int = 131072    # the design sets no limit; this bounds the server's default max_model_len
     architecture = "Safisun"
     recurrent = True      # sequences own a state slot; cached prefixes cannot be re-attached (the state is not kept)
 

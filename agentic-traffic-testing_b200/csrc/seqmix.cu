@@ -253,6 +253,27 @@ conv_state_update_kernel(const float* __restrict__ in, long long ld, int x_off, 
     }
 }
 
+// packed fp32 pairs (sm_100 FFMA2 / FMUL2): two state rows per instruction
+typedef unsigned long long f32x2;
+__device__ __forceinline__ f32x2 pk2(float lo, float hi) {
+    f32x2 v;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(v) : "f"(lo), "f"(hi));
+    return v;
+}
+__device__ __forceinline__ void upk2(f32x2 v, float& lo, float& hi) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+    f32x2 d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+    f32x2 d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+
 // ---- decayed outer-product recurrence ----------------------------------------------------------------------------
 // Per head: S_t = a_t S_(t-1) + (c_t k_t) v_t^T (S is D x V), y_t = S_t^T q_t + d v_t.
 //   a_t = decay_head[h] or decay_tok[t, h];  c_t = kscale_tok[t, h] or 1;  d = skip[h] or 0;
@@ -261,10 +282,10 @@ conv_state_update_kernel(const float* __restrict__ in, long long ld, int x_off, 
 // One CTA owns a V-tile of one head of one sequence and walks the sequence's rows in order. A thread keeps DS rows of
 // one column of S in registers for the whole walk (the state is read once and written once per step); rows are staged
 // through shared memory kChunk at a time, and the partial dot products of the D-slices are summed per chunk.
-constexpr int kRecChunk = 32;
+constexpr int kRecChunk = 16;
 
 template <int DS, bool FULL>   // FULL: D is a multiple of DS (no partial slice) and rows of q / k are 16-byte aligned
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, DS == 32 ? 2 : 1)
 linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
                          const float* __restrict__ v, long long ldv, int H, int G, int D, int V,
                          const float* __restrict__ decay_head, const float* __restrict__ decay_tok,
@@ -327,20 +348,29 @@ linear_recurrence_kernel(const float* __restrict__ q, long long ldq, const float
                 const float* ki = sk + i * D + d0;
                 float acc = 0.f;
                 if (FULL) {
-                    const float4* q4 = reinterpret_cast<const float4*>(qi);
-                    const float4* k4 = reinterpret_cast<const float4*>(ki);
+                    // state rows in pairs: S2 = a2 * S2 + k2 * v2; acc2 += S2 * q2  (three packed operations per pair),
+                    // four independent accumulators so that the dot product is not one dependent chain
+                    const ulonglong2* q4 = reinterpret_cast<const ulonglong2*>(qi);
+                    const ulonglong2* k4 = reinterpret_cast<const ulonglong2*>(ki);
+                    const f32x2 a2 = pk2(a, a), v2 = pk2(vv, vv);
+                    f32x2 ac[4] = {0ull, 0ull, 0ull, 0ull};
 #pragma unroll
                     for (int d = 0; d < DS / 4; ++d) {
-                        const float4 kk = k4[d], qq = q4[d];
-                        S[4 * d] = fmaf(a, S[4 * d], kk.x * vv);
-                        S[4 * d + 1] = fmaf(a, S[4 * d + 1], kk.y * vv);
-                        S[4 * d + 2] = fmaf(a, S[4 * d + 2], kk.z * vv);
-                        S[4 * d + 3] = fmaf(a, S[4 * d + 3], kk.w * vv);
-                        acc = fmaf(S[4 * d], qq.x, acc);
-                        acc = fmaf(S[4 * d + 1], qq.y, acc);
-                        acc = fmaf(S[4 * d + 2], qq.z, acc);
-                        acc = fmaf(S[4 * d + 3], qq.w, acc);
+                        const ulonglong2 kk = k4[d], qq = q4[d];
+                        f32x2 s0 = pk2(S[4 * d], S[4 * d + 1]), s1 = pk2(S[4 * d + 2], S[4 * d + 3]);
+                        s0 = fma2(a2, s0, mul2(kk.x, v2));
+                        s1 = fma2(a2, s1, mul2(kk.y, v2));
+                        ac[(2 * d) & 3] = fma2(s0, qq.x, ac[(2 * d) & 3]);
+                        ac[(2 * d + 1) & 3] = fma2(s1, qq.y, ac[(2 * d + 1) & 3]);
+                        upk2(s0, S[4 * d], S[4 * d + 1]);
+                        upk2(s1, S[4 * d + 2], S[4 * d + 3]);
                     }
+                    float x0, x1, x2, x3, x4, x5, x6, x7;
+                    upk2(ac[0], x0, x1);
+                    upk2(ac[1], x2, x3);
+                    upk2(ac[2], x4, x5);
+                    upk2(ac[3], x6, x7);
+                    acc = ((x0 + x1) + (x2 + x3)) + ((x4 + x5) + (x6 + x7));
                 } else {
 #pragma unroll
                     for (int d = 0; d < DS; ++d) {

@@ -60,10 +60,13 @@ class B200Backend:
         from atx.config import EngineConfig, resolve_model
         from atx.engine import AsyncEngine, LLMEngine
 
-        if dtype and dtype.lower() not in ("auto", "bfloat16", "bf16"):
+        src = resolve_model(model)
+        # model families with a true 32-bit mode (registry entries other than Llama) honour --dtype float32
+        want_f32 = bool(dtype) and dtype.lower() in ("float32", "fp32", "float") and \
+            getattr(src.config, "architecture", "llama") != "llama"
+        if dtype and dtype.lower() not in ("auto", "bfloat16", "bf16") and not want_f32:
             print(f"[llm] note: --dtype {dtype} requested; this backend computes in bfloat16 "
                   "(fp32 accumulate / residual)", flush=True)
-        src = resolve_model(model)
         self._model_path = src.path
         dp = int(os.environ.get("LLM_DP_SIZE", "1") or "1")
         ecfg = EngineConfig(
@@ -74,6 +77,7 @@ class B200Backend:
             block_size=int(os.environ.get("LLM_KV_BLOCK_SIZE") or os.environ.get("VLLM_BLOCK_SIZE") or 16),
             enable_prefix_caching=os.environ.get("LLM_PREFIX_CACHING", "1").lower() in ("1", "true", "yes", "on"),
             deterministic=os.environ.get("LLM_DETERMINISTIC", "0").lower() in ("1", "true", "yes", "on"),
+            dtype="float32" if want_f32 else "bfloat16",
         )
         self._ecfg = ecfg
         self._vocab = src.config.vocab_size
