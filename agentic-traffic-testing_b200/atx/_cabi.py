@@ -36,6 +36,7 @@ EXPORTS = [
     "atx_gemm_simple", "atx_embed_rows", "atx_concat_embed", "atx_resid_norm", "atx_gated_act", "atx_gated_norm",
     "atx_conv_dt", "atx_conv_state_update", "atx_linear_recurrence", "atx_qk_prepare", "atx_attn_local",
     "atx_attn_local_prefill", "atx_attn_local_prefill_supported",
+    "atx_linear_recurrence_chunked", "atx_linear_recurrence_chunked_supported",
 ]
 
 
@@ -107,6 +108,8 @@ def load() -> C.CDLL:
     lib.atx_conv_state_update.argtypes = [vp, i64, i32, vp, vp, vp, vp, vp, i32, i32, i32, i32, vp]
     lib.atx_linear_recurrence.argtypes = [vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp, vp,
                                           i64, vp, vp, vp, vp, i32, i32, vp]
+    lib.atx_linear_recurrence_chunked.argtypes = list(lib.atx_linear_recurrence.argtypes)
+    lib.atx_linear_recurrence_chunked_supported.argtypes = [i32]
     lib.atx_qk_prepare.argtypes = [vp, i64, i32, i32, i32, vp, vp, vp, vp, vp, vp, i32, vp, vp, vp, vp, vp, i32, i32,
                                    i32, i32, i32, i32, f32, i32, i32, vp]
     lib.atx_attn_local.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, f32, f32,

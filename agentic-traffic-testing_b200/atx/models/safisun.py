@@ -508,17 +508,36 @@ class Program:
 
     # ------------------------------------------------------------------------------------------------------------------
     def _lightning(self, l: _Layer, c: dict, proj: int, ld: int, off: int, state: torch.Tensor, out_ptr: int, ldo: int,
-                   scale: float, T: int, n_seqs: int, fl: int, st: int) -> int:
+                   scale: float, T: int, n_dec: int, n_seqs: int, fl: int, st: int) -> int:
         """proj columns [off, ...): q | k | v | g of a lightning mixer; writes the normed, gated heads to out."""
         r, lib, ck, dp = self.r, self.r.lib, self.r._ck, self.r._dp
         H, D, V = c["heads"], c["dim"], c["vdim"]
         q, k, v, g = (proj + 4 * (off + o) for o in (0, H * D, 2 * H * D, 2 * H * D + H * V))
-        ck(lib.atx_linear_recurrence(q, ld, k, ld, v, ld, H, H, D, V, l.decay.data_ptr(), None, None, None, 1,
-                                     state.data_ptr(), self.rec.data_ptr(), H * V, dp["seq_start"], dp["seq_count"],
-                                     dp["seq_pos0"], dp["seq_slot"], n_seqs, fl, st))
+        n = self._scan(q, ld, k, ld, v, ld, H, H, D, V, l.decay.data_ptr(), None, None, None, 1, state.data_ptr(),
+                       self.rec.data_ptr(), H * V, n_dec, n_seqs - n_dec, fl, st)
         ck(lib.atx_gated_norm(self.rec.data_ptr(), H * V, g, ld, l.mix_norm.data_ptr(), out_ptr, ldo, T, H * V, 1,
                               self.cfg.eps, 0, scale, self.dt, fl, st))
-        return 2
+        return n + 1
+
+    def _scan(self, q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head, decay_tok, kscale_tok, skip, act, state, y, ldy,
+              n_dec: int, n_pf: int, fl: int, st: int) -> int:
+        """The decayed outer-product recurrence of one layer over the step's sequences: single decoded tokens (the first
+        n_dec sequences) token by token on the FMA pipe; prompt portions in chunks on the tensor cores when the elements
+        are bf16 and the kernel has the key size, else token by token as well."""
+        lib, ck, dp = self.r.lib, self.r._ck, self.r._dp
+        seqs = (dp["seq_start"], dp["seq_count"], dp["seq_pos0"], dp["seq_slot"])
+        chunked = n_pf > 0 and self.xt == torch.bfloat16 and lib.atx_linear_recurrence_chunked_supported(D)
+        n_seq = n_dec if chunked else n_dec + n_pf
+        n = 0
+        if n_seq:
+            ck(lib.atx_linear_recurrence(q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head, decay_tok, kscale_tok, skip, act,
+                                         state, y, ldy, *seqs, n_seq, fl, st))
+            n += 1
+        if chunked:
+            ck(lib.atx_linear_recurrence_chunked(q, ldq, k, ldk, v, ldv, H, G, D, V, decay_head, decay_tok, kscale_tok,
+                                                 skip, act, state, y, ldy, *(p + 4 * n_dec for p in seqs), n_pf, fl, st))
+            n += 1
+        return n
 
     def forward(self, T: int, n_dec: int, n_pf: int, n_rows: int) -> int:
         """Issue every kernel of one step on the current stream; returns the launch count. The step's first n_dec
@@ -567,7 +586,7 @@ class Program:
             K_o = l.w_o.shape[1]
             mix = self.mix_flat.data_ptr()
             if l.kind == "lightning":
-                n += self._lightning(l, c, proj, ld, 0, self.state[ri], mix, K_o, 1.0, T, n_seqs, fl, st)
+                n += self._lightning(l, c, proj, ld, 0, self.state[ri], mix, K_o, 1.0, T, n_dec, n_seqs, fl, st)
             elif l.kind == "mamba2":
                 H, P, N, G, K = c["heads"], c["vdim"], c["state"], c["groups"], c["conv"]
                 inner, ch = H * P, H * P + 2 * G * N
@@ -578,13 +597,12 @@ class Program:
                                    dp["seq_start"], dp["seq_pos0"], dp["seq_slot"], T, ch, H, K, dt, fl, st))
                 ck(lib.atx_conv_state_update(proj, ld, inner, cs, dp["seq_start"], dp["seq_count"], dp["seq_pos0"],
                                              dp["seq_slot"], n_seqs, ch, K, fl, st))
-                ck(lib.atx_linear_recurrence(xbc + 4 * (inner + G * N), ch, xbc + 4 * inner, ch, xbc, ch, H, G, N, P,
-                                             None, dec, dts, l.skip.data_ptr(), 0, self.state[ri].data_ptr(),
-                                             self.rec.data_ptr(), inner, dp["seq_start"], dp["seq_count"],
-                                             dp["seq_pos0"], dp["seq_slot"], n_seqs, fl, st))
+                n += self._scan(xbc + 4 * (inner + G * N), ch, xbc + 4 * inner, ch, xbc, ch, H, G, N, P, None, dec, dts,
+                                l.skip.data_ptr(), 0, self.state[ri].data_ptr(), self.rec.data_ptr(), inner, n_dec, n_pf,
+                                fl, st)
                 ck(lib.atx_gated_norm(self.rec.data_ptr(), inner, proj, ld, l.mix_norm.data_ptr(), mix, K_o, T, inner,
                                       c["norm_groups"], eps, 1, 1.0, dt, fl, st))
-                n += 4 if K > 1 else 3
+                n += 3 if K > 1 else 2
             else:
                 a, b = c["left"], c["right"]
                 H, G, D, Vd = a["heads"], a["kv_heads"], a["dim"], a["vdim"]
@@ -617,7 +635,7 @@ class Program:
                     n += 1
                 n += 1
                 n += self._lightning(l, b, proj, ld, o_right, self.state[ri], mix + H * Vd * self.esz, K_o,
-                                     float(c["right_scale"]), T, n_seqs, fl, st)
+                                     float(c["right_scale"]), T, n_dec, n_seqs, fl, st)
             lin["o"].run(y, W, T, fl, st, zeroed=small)
             n += 1
             pending = l.norm1b.data_ptr()

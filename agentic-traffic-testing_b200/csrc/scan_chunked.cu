@@ -1,0 +1,329 @@
+// The decayed outer-product recurrence of seqmix.cu for prompt portions, in its chunk-parallel form on the tensor cores.
+//
+//   S_t = a_t S_(t-1) + (c_t k_t) v_t^T,   y_t = S_t^T q_t + d v_t          (S: D x V per head, fp32)
+//
+// Over a chunk of C = 64 consecutive tokens with L_t = sum_{u <= t} log a_u (inside the chunk) and S_in the state before
+// its first token:
+//
+//   y_t   = e^{L_t} S_in^T q_t  +  sum_{j <= t} e^{L_t - L_j} c_j (q_t . k_j) v_j
+//   S_out = e^{L_last} S_in     +  sum_j e^{L_last - L_j} c_j k_j v_j^T
+//
+// so the work of a chunk is four small matrix products (Q K^T, P V, Q S_in, K^T V~) on mma.sync m16n8k16 with bf16
+// operands and fp32 accumulation. What stays fp32: the state (it lives in accumulator registers for the whole portion
+// and is read out as a bf16 high part plus a bf16 remainder, two MMAs, so the read-out keeps ~16 bits), the logarithms,
+// their running sums and every exponential, the step sizes c_t; the decay weights multiply fp32 accumulators or fp32
+// inputs before the one rounding to bf16 that any tensor-core operand gets. Every exponent is a difference L_t - L_j
+// with j <= t, hence <= 0: nothing overflows however strong the decay. log a_t is clamped at -80 (a_t = 0 would make
+// the differences undefined; e^-80 of a state is below fp32 resolution of anything added to it).
+//
+// One CTA = one sequence x one head x 64 value columns; warp w owns 16 of them. The state tile is kept TRANSPOSED
+// (rows = value columns, columns = key dimensions) so that the accumulator fragments of S^T turn into A fragments of
+// S^T Q^T in registers, as a softmax kernel turns its probabilities into the A operand of P V. Sequences are walked as
+// in seqmix.cu: rows [seq_start, seq_start + seq_count), state slot seq_slot, zero state when seq_pos0 == 0.
+#include "common.cuh"
+
+#include "../../include/atx_b200.h"
+
+namespace atx {
+
+constexpr int kScC = 64;   // tokens per chunk
+constexpr int kScV = 64;   // value columns per CTA
+
+__device__ __forceinline__ float silu_sc(float x) { return x / (1.f + expf(-x)); }
+
+template <int D>
+__global__ void __launch_bounds__(128)
+scan_chunked_kernel(const float* __restrict__ q, long long ldq, const float* __restrict__ k, long long ldk,
+                    const float* __restrict__ v, long long ldv, int H, int G, int V,
+                    const float* __restrict__ decay_head, const float* __restrict__ decay_tok,
+                    const float* __restrict__ kscale_tok, const float* __restrict__ skip, int act,
+                    float* __restrict__ state, float* __restrict__ y, long long ldy,
+                    const int* __restrict__ seq_start, const int* __restrict__ seq_count,
+                    const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot) {
+    constexpr int LQ = D + 8, LV = kScV + 8, LP = kScC + 8;   // padded rows: ldmatrix without bank conflicts
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [C][D]
+    __nv_bfloat16* sK = sQ + kScC * LQ;                               // [C][D]
+    __nv_bfloat16* sV = sK + kScC * LQ;                               // [C][64]  v_j
+    __nv_bfloat16* sW = sV + kScC * LV;                               // [C][64]  e^{L_last - L_j} c_j v_j
+    __nv_bfloat16* sP = sW + kScC * LV;                               // [C][C]   e^{L_t - L_j} c_j (q_t . k_j), j <= t
+    float* sL = reinterpret_cast<float*>(sP + kScC * LP);             // [C] running sums of log a, per half of the chunk
+    float* sC = sL + kScC;                                            // [C] c_j (0 for rows past the portion)
+    pdl_launch_dependents();
+    pdl_wait();
+    const int s = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * kScV;
+    const int n = seq_count[s];
+    if (n <= 0) return;
+    const long long r0 = seq_start[s];
+    const int g = h / (H / G);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int vw = warp * 16;
+    const int vr = v0 + vw + (lane >> 2);        // value column of accumulator elements 0, 1 (elements 2, 3: + 8)
+    const int c2 = 2 * (lane & 3);               // first of this thread's two columns inside an 8-wide tile
+
+    float S[D / 8][4];
+    float* st = state + (static_cast<long long>(seq_slot[s]) * H + h) * D * V;
+    const bool fresh = seq_pos0[s] == 0;
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int vv = vr + 8 * (e >> 1), d = nd * 8 + c2 + (e & 1);
+            S[nd][e] = (!fresh && vv < V) ? st[static_cast<long long>(d) * V + vv] : 0.f;
+        }
+    const float la_head = decay_head ? fmaxf(logf(decay_head[h]), -80.f) : 0.f;
+    const float dskip = skip ? skip[h] : 0.f;
+    auto Lc = [&](int t) { return sL[t] + (t >= 32 ? sL[31] : 0.f); };
+
+    for (int c0 = 0; c0 < n; c0 += kScC) {
+        const int cn = min(kScC, n - c0);
+        __syncthreads();   // the previous chunk's tiles have been consumed
+        if (threadIdx.x < kScC) {
+            const int t = threadIdx.x;
+            float la = 0.f, c = 0.f;   // rows past the portion: no decay, no contribution
+            if (t < cn) {
+                la = decay_tok ? fmaxf(logf(decay_tok[(r0 + c0 + t) * H + h]), -80.f) : la_head;
+                c = kscale_tok ? kscale_tok[(r0 + c0 + t) * H + h] : 1.f;
+            }
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const float x = __shfl_up_sync(0xffffffffu, la, o);
+                if (lane >= o) la += x;
+            }
+            sL[t] = la;
+            sC[t] = c;
+        }
+        __syncthreads();
+        const float Llast = Lc(kScC - 1);
+        for (int e = threadIdx.x; e < kScC * D; e += 128) {
+            const int i = e / D, d = e - i * D;
+            float qv = 0.f, kv = 0.f;
+            if (i < cn) {
+                const long long row = r0 + c0 + i;
+                qv = q[row * ldq + g * D + d];
+                kv = k[row * ldk + g * D + d];
+                if (act) {
+                    qv = silu_sc(qv);
+                    kv = silu_sc(kv);
+                }
+            }
+            sQ[i * LQ + d] = __float2bfloat16_rn(qv);
+            sK[i * LQ + d] = __float2bfloat16_rn(kv);
+        }
+        for (int e = threadIdx.x; e < kScC * kScV; e += 128) {
+            const int i = e / kScV, j = e - i * kScV;
+            float vv = 0.f;
+            if (i < cn && v0 + j < V) {
+                vv = v[(r0 + c0 + i) * ldv + static_cast<long long>(h) * V + v0 + j];
+                if (act) vv = silu_sc(vv);
+            }
+            sV[i * LV + j] = __float2bfloat16_rn(vv);
+            sW[i * LV + j] = __float2bfloat16_rn(vv * (expf(Llast - Lc(i)) * sC[i]));
+        }
+        __syncthreads();
+
+        // ---- what the state before the chunk contributes: Y^T = S_in^T Q^T, column t scaled by e^{L_t} ------------
+        float acc[kScC / 8][4];
+#pragma unroll
+        for (int i = 0; i < kScC / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        if (!(fresh && c0 == 0)) {
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t ah[4], al[4];
+#pragma unroll
+                for (int f = 0; f < 4; ++f) {
+                    const float x0 = S[2 * kk + (f >> 1)][2 * (f & 1)], x1 = S[2 * kk + (f >> 1)][2 * (f & 1) + 1];
+                    ah[f] = pack_bf16(x0, x1);
+                    al[f] = pack_bf16(x0 - bf16lo(ah[f]), x1 - bf16hi(ah[f]));
+                }
+#pragma unroll
+                for (int nb2 = 0; nb2 < kScC / 16; ++nb2) {
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(smem_u32(sQ + (nb2 * 16 + (lane >> 4) * 8 + (lane & 7)) * LQ + kk * 16 + ((lane >> 3) & 1) * 8),
+                            b0, b1, b2, b3);
+                    mma_bf16(acc[2 * nb2], ah, b0, b1);
+                    mma_bf16(acc[2 * nb2 + 1], ah, b2, b3);
+                    mma_bf16(acc[2 * nb2], al, b0, b1);
+                    mma_bf16(acc[2 * nb2 + 1], al, b2, b3);
+                }
+            }
+#pragma unroll
+            for (int nb = 0; nb < kScC / 8; ++nb) {
+                const float e0 = expf(Lc(nb * 8 + c2)), e1 = expf(Lc(nb * 8 + c2 + 1));
+                acc[nb][0] *= e0;
+                acc[nb][1] *= e1;
+                acc[nb][2] *= e0;
+                acc[nb][3] *= e1;
+            }
+        }
+
+        // ---- P: this warp's 16 rows of (Q K^T) with the decay between key and query, keys after the query dropped ---
+        {
+            float sc[kScC / 8][4];
+#pragma unroll
+            for (int i = 0; i < kScC / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < D / 16; ++ks) {
+                uint32_t qf[4];
+                ldsm_x4(smem_u32(sQ + (warp * 16 + (lane & 15)) * LQ + ks * 16 + (lane >> 4) * 8), qf[0], qf[1], qf[2],
+                        qf[3]);
+#pragma unroll
+                for (int nb2 = 0; nb2 < kScC / 16; ++nb2) {
+                    if (nb2 > warp) continue;   // every key of the tile lies after this warp's rows (warp-uniform)
+                    uint32_t b0, b1, b2, b3;
+                    ldsm_x4(smem_u32(sK + (nb2 * 16 + (lane >> 4) * 8 + (lane & 7)) * LQ + ks * 16 + ((lane >> 3) & 1) * 8),
+                            b0, b1, b2, b3);
+                    mma_bf16(sc[2 * nb2], qf, b0, b1);
+                    mma_bf16(sc[2 * nb2 + 1], qf, b2, b3);
+                }
+            }
+            const int t0 = warp * 16 + (lane >> 2);
+            const float Lt0 = Lc(t0), Lt1 = Lc(t0 + 8);
+#pragma unroll
+            for (int nb = 0; nb < kScC / 8; ++nb) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int t = t0 + 8 * (e >> 1), j = nb * 8 + c2 + (e & 1);
+                    p[e] = (j <= t) ? sc[nb][e] * (expf(((e >> 1) ? Lt1 : Lt0) - Lc(j)) * sC[j]) : 0.f;
+                }
+                *reinterpret_cast<uint32_t*>(sP + t0 * LP + nb * 8 + c2) = pack_bf16(p[0], p[1]);
+                *reinterpret_cast<uint32_t*>(sP + (t0 + 8) * LP + nb * 8 + c2) = pack_bf16(p[2], p[3]);
+            }
+        }
+        __syncthreads();
+
+        // ---- inside the chunk: Y^T += V^T P^T -------------------------------------------------------------------------
+#pragma unroll
+        for (int kk = 0; kk < kScC / 16; ++kk) {
+            uint32_t a[4];
+            ldsm_x4_t(smem_u32(sV + (kk * 16 + (lane >> 4) * 8 + (lane & 7)) * LV + vw + ((lane >> 3) & 1) * 8), a[0], a[1],
+                      a[2], a[3]);
+#pragma unroll
+            for (int nb2 = 0; nb2 < kScC / 16; ++nb2) {
+                if (kk > nb2) continue;   // keys after every query of the tile
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(sP + (nb2 * 16 + (lane >> 4) * 8 + (lane & 7)) * LP + kk * 16 + ((lane >> 3) & 1) * 8), b0,
+                        b1, b2, b3);
+                mma_bf16(acc[2 * nb2], a, b0, b1);
+                mma_bf16(acc[2 * nb2 + 1], a, b2, b3);
+            }
+        }
+#pragma unroll
+        for (int nb = 0; nb < kScC / 8; ++nb)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int t = nb * 8 + c2 + (e & 1), vv = vr + 8 * (e >> 1);
+                if (t >= cn || vv >= V) continue;
+                const long long row = r0 + c0 + t;
+                float out = acc[nb][e];
+                if (skip) {
+                    float x = v[row * ldv + static_cast<long long>(h) * V + vv];
+                    if (act) x = silu_sc(x);
+                    out = fmaf(dskip, x, out);
+                }
+                y[row * ldy + static_cast<long long>(h) * V + vv] = out;
+            }
+
+        // ---- the state after the chunk: S^T = e^{L_last} S^T + V~^T K ------------------------------------------------
+        const float dl = expf(Llast);
+#pragma unroll
+        for (int nd = 0; nd < D / 8; ++nd) {
+            S[nd][0] *= dl;
+            S[nd][1] *= dl;
+            S[nd][2] *= dl;
+            S[nd][3] *= dl;
+        }
+#pragma unroll
+        for (int kk = 0; kk < kScC / 16; ++kk) {
+            if (kk * 16 >= cn) continue;   // rows past the portion are zero
+            uint32_t a[4];
+            ldsm_x4_t(smem_u32(sW + (kk * 16 + (lane >> 4) * 8 + (lane & 7)) * LV + vw + ((lane >> 3) & 1) * 8), a[0], a[1],
+                      a[2], a[3]);
+#pragma unroll
+            for (int nb2 = 0; nb2 < D / 16; ++nb2) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4_t(smem_u32(sK + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * LQ + nb2 * 16 + (lane >> 4) * 8), b0,
+                          b1, b2, b3);
+                mma_bf16(S[2 * nb2], a, b0, b1);
+                mma_bf16(S[2 * nb2 + 1], a, b2, b3);
+            }
+        }
+    }
+#pragma unroll
+    for (int nd = 0; nd < D / 8; ++nd)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int vv = vr + 8 * (e >> 1), d = nd * 8 + c2 + (e & 1);
+            if (vv < V) st[static_cast<long long>(d) * V + vv] = S[nd][e];
+        }
+}
+
+template <int D>
+static int launch_scan_chunked(const float* q, long long ldq, const float* k, long long ldk, const float* v, long long ldv,
+                               int H, int G, int V, const float* decay_head, const float* decay_tok,
+                               const float* kscale_tok, const float* skip, int act, float* state, float* y,
+                               long long ldy, const int* seq_start, const int* seq_count, const int* seq_pos0,
+                               const int* seq_slot, int n_seqs, int flags, cudaStream_t stream) {
+    const int smem = 2 * kScC * (D + 8) * 2 + 2 * kScC * (kScV + 8) * 2 + kScC * (kScC + 8) * 2 + 2 * kScC * 4;
+    static bool attr_done = false;
+    if (!attr_done && smem > 48 * 1024) {
+        ATX_CUDA(cudaFuncSetAttribute(scan_chunked_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        attr_done = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    cfg.gridDim = dim3(n_seqs, H, (V + kScV - 1) / kScV);
+    cfg.blockDim = dim3(128);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    if (flags & ATX_FLAG_PDL) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, scan_chunked_kernel<D>, q, ldq, k, ldk, v, ldv, H, G, V, decay_head, decay_tok,
+                                kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0, seq_slot));
+    return ATX_OK;
+}
+
+}  // namespace atx
+
+using namespace atx;
+
+extern "C" {
+
+int atx_linear_recurrence_chunked_supported(int D) {
+    return (D == 16 || D == 32 || D == 48 || D == 64 || D == 96 || D == 128) ? 1 : 0;
+}
+
+int atx_linear_recurrence_chunked(const float* q, long long ldq, const float* k, long long ldk, const float* v,
+                                  long long ldv, int H, int G, int D, int V, const float* decay_head,
+                                  const float* decay_tok, const float* kscale_tok, const float* skip, int act,
+                                  float* state, float* y, long long ldy, const int* seq_start, const int* seq_count,
+                                  const int* seq_pos0, const int* seq_slot, int n_seqs, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k && v && state && y && seq_start && seq_count && seq_pos0 && seq_slot,
+                "atx_linear_recurrence_chunked: null pointer");
+    ATX_REQUIRE((decay_head != nullptr) != (decay_tok != nullptr),
+                "atx_linear_recurrence_chunked: exactly one of decay_head / decay_tok");
+    ATX_REQUIRE(n_seqs > 0 && H > 0 && G > 0 && H % G == 0 && V > 0 && atx_linear_recurrence_chunked_supported(D),
+                "atx_linear_recurrence_chunked: bad shape n_seqs=%d H=%d G=%d D=%d V=%d", n_seqs, H, G, D, V);
+    cudaStream_t cs = reinterpret_cast<cudaStream_t>(stream);
+#define ATX_SCAN_CASE(D_)                                                                                                \
+    case D_:                                                                                                             \
+        return launch_scan_chunked<D_>(q, ldq, k, ldk, v, ldv, H, G, V, decay_head, decay_tok, kscale_tok, skip, act,   \
+                                       state, y, ldy, seq_start, seq_count, seq_pos0, seq_slot, n_seqs, flags, cs)
+    switch (D) {
+        ATX_SCAN_CASE(16);
+        ATX_SCAN_CASE(32);
+        ATX_SCAN_CASE(48);
+        ATX_SCAN_CASE(64);
+        ATX_SCAN_CASE(96);
+        ATX_SCAN_CASE(128);
+    }
+#undef ATX_SCAN_CASE
+    return ATX_OK;
+}
+
+}  // extern "C"

@@ -264,6 +264,16 @@ int atx_linear_recurrence(const float* q, long long ldq, const float* k, long lo
                           const float* kscale_tok, const float* skip, int act, float* state, float* y, long long ldy,
                           const int* seq_start, const int* seq_count, const int* seq_pos0, const int* seq_slot,
                           int n_seqs, int flags, atx_stream_t stream);
+/* The same recurrence for prompt portions in its chunk-parallel form on the tensor cores (chunks of 64 tokens: the
+ * products inside a chunk and with the state before it are bf16 MMAs with fp32 accumulation; state, logarithms of the
+ * decays, their running sums, exponentials and step sizes stay fp32). Same arguments, same state layout, so a sequence
+ * may switch between the two from step to step. D must be one of the sizes ..._supported() accepts. */
+int atx_linear_recurrence_chunked_supported(int D);
+int atx_linear_recurrence_chunked(const float* q, long long ldq, const float* k, long long ldk, const float* v,
+                                  long long ldv, int H, int G, int D, int V, const float* decay_head,
+                                  const float* decay_tok, const float* kscale_tok, const float* skip, int act,
+                                  float* state, float* y, long long ldy, const int* seq_start, const int* seq_count,
+                                  const int* seq_pos0, const int* seq_slot, int n_seqs, int flags, atx_stream_t stream);
 /* q/k/v of one step from a fused projection (fp32, row pitch ld, column offsets): + bias (nullable), RMS norm over the
  * WHOLE q and the whole k projection with weights wq [H D] / wk [G D] (nullable: no norm), rotation of adjacent pairs
  * (2i, 2i+1) of the first rot_dims dimensions of every head by the angles of table rot [max_pos, rot_dims] (cosines,

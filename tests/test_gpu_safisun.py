@@ -412,6 +412,72 @@ def test_recurrence_remembers_a_far_key_across_steps_and_slots(per_token):
     assert float(((got - want).abs() / scale).max()) < 2e-4
 
 
+@pytest.mark.parametrize("per_token,D,V", [(False, 32, 24), (False, 128, 128), (False, 64, 80), (True, 128, 64),
+                                            (True, 16, 40), (True, 96, 8)])
+def test_chunked_recurrence_matches_the_closed_form_and_shares_its_state_with_the_stepwise_kernel(per_token, D, V):
+    """The tensor-core form of the recurrence on the far-key input: portions of uneven sizes (chunk edges inside and at
+    the ends of portions, a portion of two tokens), single tokens between them on the token-by-token kernel, the same
+    state slot throughout, a second sequence beside one portion, slots filled with garbage first. Operands are bf16
+    values, so what remains against the float64 closed form is the rounding of the decayed products. One head decays
+    to exactly zero in a single step (per-token case): nothing may turn into NaN."""
+    lib, cabi = _lib()
+    assert lib.atx_linear_recurrence_chunked_supported(D) == 1 and lib.atx_linear_recurrence_chunked_supported(40) == 0
+    n, H, G = 450, 4, 2
+    g = torch.Generator().manual_seed(5)
+    bf = lambda x: x.to(torch.bfloat16).to(F64)
+    q, k = bf(torch.randn(n, G, D, generator=g, dtype=F64)), bf(torch.randn(n, G, D, generator=g, dtype=F64))
+    v = bf(torch.randn(n, H, V, generator=g, dtype=F64))
+    k[3], v[3] = bf(k[3] * 30.0), bf(v[3] * 30.0)
+    q[-50:] = q[-50:].abs() * torch.sign(k[3])
+    qh, kh = q.repeat_interleave(H // G, 1), k.repeat_interleave(H // G, 1)
+    if per_token:
+        dt = (0.01 + 0.05 * torch.rand(n, H, generator=g)).to(F64)
+        rate, skip = torch.tensor([0.01, 0.3, 2.0, 1e5], dtype=F64), torch.tensor([0.5, -1.0, 0.0, 2.0], dtype=F64)
+        dec = torch.exp(-rate * dt).float()
+        assert float(dec[:, 3].max()) == 0.0
+        want = R.selective_scan(v, kh, qh, dt, rate, skip)
+        dec_d, dt_d, skip_d = dec.to(DEV).contiguous(), dt.float().to(DEV).contiguous(), skip.float().to(DEV)
+    else:
+        lam = torch.tensor([0.9995, 0.99, 0.9, 0.5], dtype=F64)
+        want = R.decayed_linear_attention(qh, kh, v, lam)
+        lam_d = lam.float().to(DEV)
+    assert want[-1, 0].abs().max() > 20 * want[2, 0].abs().max()          # the far token dominates the end
+    other = 70
+    qa, ka, va = (x.float().reshape(n, -1).to(DEV) for x in (q, k, v))
+    state = torch.full((3, H, D, V), 1e30, device=DEV)
+    cuts, at, outs = [2, 62, 1, 64, 65, 1, 1, 127, 3], 0, []
+    cuts.append(n - sum(cuts))
+    for i, c in enumerate(cuts):
+        with_other = i == 4
+        src = (list(range(other)) if with_other else []) + list(range(at, at + c))
+        idx = torch.tensor(src, device=DEV)
+        qs, ks, vs = qa[idx].contiguous(), ka[idx].contiguous(), va[idx].contiguous()
+        y = torch.full((len(src), H * V), float("nan"), device=DEV)
+        seqs = ([(0, other, 0, 0)] if with_other else []) + [(len(src) - c, c, at, 2)]
+        a = [_i32([s_[j] for s_ in seqs]) for j in range(4)]
+        fn = lib.atx_linear_recurrence if c == 1 else lib.atx_linear_recurrence_chunked
+        if per_token:
+            dr, tr = dec_d[idx].contiguous(), dt_d[idx].contiguous()
+            rc = fn(qs.data_ptr(), G * D, ks.data_ptr(), G * D, vs.data_ptr(), H * V, H, G, D, V, None, dr.data_ptr(),
+                    tr.data_ptr(), skip_d.data_ptr(), 0, state.data_ptr(), y.data_ptr(), H * V, a[0].data_ptr(),
+                    a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), len(seqs), 0, _st())
+        else:
+            rc = fn(qs.data_ptr(), G * D, ks.data_ptr(), G * D, vs.data_ptr(), H * V, H, G, D, V, lam_d.data_ptr(), None,
+                    None, None, 0, state.data_ptr(), y.data_ptr(), H * V, a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(),
+                    a[3].data_ptr(), len(seqs), 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        torch.cuda.synchronize()
+        outs.append(y.cpu().double())
+        at += c
+    assert all(bool(torch.isfinite(o).all()) for o in outs)
+    scale = want.abs().amax(dim=2, keepdim=True).clamp(min=1.0)
+    beside = outs[4][:other].view(other, H, V)
+    assert float(((beside - want[:other]).abs() / scale[:other]).max()) < 2e-2
+    got = torch.cat([o[-c:] for o, c in zip(outs, cuts)]).view(n, H, V)
+    assert float(((got - want).abs() / scale).max()) < 2e-2
+    assert float(((got - want).abs() / scale).mean()) < 2e-3
+
+
 def test_short_convolution_carries_its_window_across_short_steps():
     lib, cabi = _lib()
     n, Cc, H, K = 29, 37, 3, 4
