@@ -39,7 +39,7 @@ scan_chunked_kernel(const float* __restrict__ q, long long ldq, const float* __r
                     const float* __restrict__ kscale_tok, const float* __restrict__ skip, int act,
                     float* __restrict__ state, float* __restrict__ y, long long ldy,
                     const int* __restrict__ seq_start, const int* __restrict__ seq_count,
-                    const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot) {
+                    const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int vec) {
     constexpr int LQ = D + 8, LV = kScV + 8, LP = kScC + 8;   // padded rows: ldmatrix without bank conflicts
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [C][D]
@@ -95,30 +95,100 @@ scan_chunked_kernel(const float* __restrict__ q, long long ldq, const float* __r
         }
         __syncthreads();
         const float Llast = Lc(kScC - 1);
-        for (int e = threadIdx.x; e < kScC * D; e += 128) {
-            const int i = e / D, d = e - i * D;
-            float qv = 0.f, kv = 0.f;
-            if (i < cn) {
-                const long long row = r0 + c0 + i;
-                qv = q[row * ldq + g * D + d];
-                kv = k[row * ldk + g * D + d];
-                if (act) {
-                    qv = silu_sc(qv);
-                    kv = silu_sc(kv);
+        // Tiles: loads are issued in batches ahead of their use (a chunk is short, so memory latency is what a naive
+        // element loop would spend its time on); 16-byte loads when pointers, pitches and sizes allow.
+        if (vec & 1) {
+            constexpr int IT = kScC * D / 4 / 128, U = (IT % 4 == 0) ? 4 : 2;
+#pragma unroll 1
+            for (int it = 0; it < IT; it += U) {
+                float4 xq[U], xk[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / (D / 4), d = (e - i * (D / 4)) * 4;
+                    xq[u] = xk[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (i < cn) {
+                        xq[u] = *reinterpret_cast<const float4*>(q + (r0 + c0 + i) * ldq + g * D + d);
+                        xk[u] = *reinterpret_cast<const float4*>(k + (r0 + c0 + i) * ldk + g * D + d);
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / (D / 4), d = (e - i * (D / 4)) * 4;
+                    if (act) {
+                        xq[u] = make_float4(silu_sc(xq[u].x), silu_sc(xq[u].y), silu_sc(xq[u].z), silu_sc(xq[u].w));
+                        xk[u] = make_float4(silu_sc(xk[u].x), silu_sc(xk[u].y), silu_sc(xk[u].z), silu_sc(xk[u].w));
+                    }
+                    *reinterpret_cast<uint2*>(sQ + i * LQ + d) = make_uint2(pack_bf16(xq[u].x, xq[u].y), pack_bf16(xq[u].z, xq[u].w));
+                    *reinterpret_cast<uint2*>(sK + i * LQ + d) = make_uint2(pack_bf16(xk[u].x, xk[u].y), pack_bf16(xk[u].z, xk[u].w));
                 }
             }
-            sQ[i * LQ + d] = __float2bfloat16_rn(qv);
-            sK[i * LQ + d] = __float2bfloat16_rn(kv);
-        }
-        for (int e = threadIdx.x; e < kScC * kScV; e += 128) {
-            const int i = e / kScV, j = e - i * kScV;
-            float vv = 0.f;
-            if (i < cn && v0 + j < V) {
-                vv = v[(r0 + c0 + i) * ldv + static_cast<long long>(h) * V + v0 + j];
-                if (act) vv = silu_sc(vv);
+        } else {
+            constexpr int IT = kScC * D / 128, U = 8;
+#pragma unroll 1
+            for (int it = 0; it < IT; it += U) {
+                float xq[U], xk[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / D, d = e - i * D;
+                    xq[u] = xk[u] = 0.f;
+                    if (i < cn) {
+                        xq[u] = q[(r0 + c0 + i) * ldq + g * D + d];
+                        xk[u] = k[(r0 + c0 + i) * ldk + g * D + d];
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / D, d = e - i * D;
+                    if (act) {
+                        xq[u] = silu_sc(xq[u]);
+                        xk[u] = silu_sc(xk[u]);
+                    }
+                    sQ[i * LQ + d] = __float2bfloat16_rn(xq[u]);
+                    sK[i * LQ + d] = __float2bfloat16_rn(xk[u]);
+                }
             }
-            sV[i * LV + j] = __float2bfloat16_rn(vv);
-            sW[i * LV + j] = __float2bfloat16_rn(vv * (expf(Llast - Lc(i)) * sC[i]));
+        }
+        if (vec & 2) {
+            constexpr int IT = kScC * kScV / 4 / 128, U = 4;
+#pragma unroll 1
+            for (int it = 0; it < IT; it += U) {
+                float4 xv[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / (kScV / 4), j = (e - i * (kScV / 4)) * 4;
+                    xv[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (i < cn && v0 + j < V)
+                        xv[u] = *reinterpret_cast<const float4*>(v + (r0 + c0 + i) * ldv + static_cast<long long>(h) * V + v0 + j);
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / (kScV / 4), j = (e - i * (kScV / 4)) * 4;
+                    if (act) xv[u] = make_float4(silu_sc(xv[u].x), silu_sc(xv[u].y), silu_sc(xv[u].z), silu_sc(xv[u].w));
+                    const float w = expf(Llast - Lc(i)) * sC[i];
+                    *reinterpret_cast<uint2*>(sV + i * LV + j) = make_uint2(pack_bf16(xv[u].x, xv[u].y), pack_bf16(xv[u].z, xv[u].w));
+                    *reinterpret_cast<uint2*>(sW + i * LV + j) =
+                        make_uint2(pack_bf16(xv[u].x * w, xv[u].y * w), pack_bf16(xv[u].z * w, xv[u].w * w));
+                }
+            }
+        } else {
+            constexpr int IT = kScC * kScV / 128, U = 8;
+#pragma unroll 1
+            for (int it = 0; it < IT; it += U) {
+                float xv[U];
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / kScV, j = e - i * kScV;
+                    xv[u] = 0.f;
+                    if (i < cn && v0 + j < V) xv[u] = v[(r0 + c0 + i) * ldv + static_cast<long long>(h) * V + v0 + j];
+                }
+#pragma unroll
+                for (int u = 0; u < U; ++u) {
+                    const int e = threadIdx.x + (it + u) * 128, i = e / kScV, j = e - i * kScV;
+                    if (act) xv[u] = silu_sc(xv[u]);
+                    sV[i * LV + j] = __float2bfloat16_rn(xv[u]);
+                    sW[i * LV + j] = __float2bfloat16_rn(xv[u] * (expf(Llast - Lc(i)) * sC[i]));
+                }
+            }
         }
         __syncthreads();
 
@@ -210,20 +280,22 @@ scan_chunked_kernel(const float* __restrict__ q, long long ldq, const float* __r
             }
         }
 #pragma unroll
-        for (int nb = 0; nb < kScC / 8; ++nb)
+        for (int nb = 0; nb < kScC / 8; nb += 2) {
+            float xs[8];
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int t = nb * 8 + c2 + (e & 1), vv = vr + 8 * (e >> 1);
-                if (t >= cn || vv >= V) continue;
-                const long long row = r0 + c0 + t;
-                float out = acc[nb][e];
-                if (skip) {
-                    float x = v[row * ldv + static_cast<long long>(h) * V + vv];
-                    if (act) x = silu_sc(x);
-                    out = fmaf(dskip, x, out);
-                }
-                y[row * ldy + static_cast<long long>(h) * V + vv] = out;
+            for (int f = 0; f < 8; ++f) {
+                const int t = (nb + (f >> 2)) * 8 + c2 + (f & 1), vv = vr + 8 * ((f >> 1) & 1);
+                xs[f] = (skip && t < cn && vv < V) ? v[(r0 + c0 + t) * ldv + static_cast<long long>(h) * V + vv] : 0.f;
             }
+#pragma unroll
+            for (int f = 0; f < 8; ++f) {
+                const int t = (nb + (f >> 2)) * 8 + c2 + (f & 1), vv = vr + 8 * ((f >> 1) & 1);
+                if (t >= cn || vv >= V) continue;
+                float out = acc[nb + (f >> 2)][f & 3];
+                if (skip) out = fmaf(dskip, act ? silu_sc(xs[f]) : xs[f], out);
+                y[(r0 + c0 + t) * ldy + static_cast<long long>(h) * V + vv] = out;
+            }
+        }
 
         // ---- the state after the chunk: S^T = e^{L_last} S^T + V~^T K ------------------------------------------------
         const float dl = expf(Llast);
@@ -283,8 +355,12 @@ static int launch_scan_chunked(const float* q, long long ldq, const float* k, lo
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
+    // bit 0: q / k rows can be read 16 bytes at a time; bit 1: v rows
+    auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const int vec = ((al16(q) && al16(k) && ldq % 4 == 0 && ldk % 4 == 0) ? 1 : 0) |
+                    ((al16(v) && ldv % 4 == 0 && V % 4 == 0) ? 2 : 0);
     ATX_CUDA(cudaLaunchKernelEx(&cfg, scan_chunked_kernel<D>, q, ldq, k, ldk, v, ldv, H, G, V, decay_head, decay_tok,
-                                kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0, seq_slot));
+                                kscale_tok, skip, act, state, y, ldy, seq_start, seq_count, seq_pos0, seq_slot, vec));
     return ATX_OK;
 }
 

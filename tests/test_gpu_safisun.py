@@ -447,24 +447,28 @@ def test_chunked_recurrence_matches_the_closed_form_and_shares_its_state_with_th
     state = torch.full((3, H, D, V), 1e30, device=DEV)
     cuts, at, outs = [2, 62, 1, 64, 65, 1, 1, 127, 3], 0, []
     cuts.append(n - sum(cuts))
+    lead = 1 if D in (32, 96) else 4       # unused elements before every row: an odd pitch and 4-byte alignment, or 16
     for i, c in enumerate(cuts):
         with_other = i == 4
         src = (list(range(other)) if with_other else []) + list(range(at, at + c))
         idx = torch.tensor(src, device=DEV)
-        qs, ks, vs = qa[idx].contiguous(), ka[idx].contiguous(), va[idx].contiguous()
+        # lead 1: the kernel's 4-byte loads; lead 4: its 16-byte loads
+        qs, ks, vs = (torch.nn.functional.pad(x[idx], (lead, 0)) for x in (qa, ka, va))
+        qp, kp, vp = (x.data_ptr() + 4 * lead for x in (qs, ks, vs))
+        lq, lv = G * D + lead, H * V + lead
         y = torch.full((len(src), H * V), float("nan"), device=DEV)
         seqs = ([(0, other, 0, 0)] if with_other else []) + [(len(src) - c, c, at, 2)]
         a = [_i32([s_[j] for s_ in seqs]) for j in range(4)]
         fn = lib.atx_linear_recurrence if c == 1 else lib.atx_linear_recurrence_chunked
         if per_token:
             dr, tr = dec_d[idx].contiguous(), dt_d[idx].contiguous()
-            rc = fn(qs.data_ptr(), G * D, ks.data_ptr(), G * D, vs.data_ptr(), H * V, H, G, D, V, None, dr.data_ptr(),
-                    tr.data_ptr(), skip_d.data_ptr(), 0, state.data_ptr(), y.data_ptr(), H * V, a[0].data_ptr(),
-                    a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), len(seqs), 0, _st())
+            rc = fn(qp, lq, kp, lq, vp, lv, H, G, D, V, None, dr.data_ptr(), tr.data_ptr(), skip_d.data_ptr(), 0,
+                    state.data_ptr(), y.data_ptr(), H * V, a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(),
+                    len(seqs), 0, _st())
         else:
-            rc = fn(qs.data_ptr(), G * D, ks.data_ptr(), G * D, vs.data_ptr(), H * V, H, G, D, V, lam_d.data_ptr(), None,
-                    None, None, 0, state.data_ptr(), y.data_ptr(), H * V, a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(),
-                    a[3].data_ptr(), len(seqs), 0, _st())
+            rc = fn(qp, lq, kp, lq, vp, lv, H, G, D, V, lam_d.data_ptr(), None, None, None, 0, state.data_ptr(),
+                    y.data_ptr(), H * V, a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), len(seqs), 0,
+                    _st())
         assert rc == 0, lib.atx_last_error()
         torch.cuda.synchronize()
         outs.append(y.cpu().double())
