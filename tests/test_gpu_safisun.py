@@ -413,7 +413,7 @@ def test_recurrence_remembers_a_far_key_across_steps_and_slots(per_token):
 
 
 @pytest.mark.parametrize("per_token,D,V", [(False, 32, 24), (False, 128, 128), (False, 64, 80), (True, 128, 64),
-                                            (True, 16, 40), (True, 96, 8)])
+                                            (True, 32, 40), (True, 96, 8)])
 def test_chunked_recurrence_matches_the_closed_form_and_shares_its_state_with_the_stepwise_kernel(per_token, D, V):
     """The tensor-core form of the recurrence on the far-key input: portions of uneven sizes (chunk edges inside and at
     the ends of portions, a portion of two tokens), single tokens between them on the token-by-token kernel, the same
