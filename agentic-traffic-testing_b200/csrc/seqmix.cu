@@ -226,6 +226,90 @@ conv_dt_kernel(const float* __restrict__ in, long long ld, int x_off, int dt_off
     }
 }
 
+// The same for prompt-sized steps: a CTA takes kConvRows consecutive rows x 256 channels and every thread walks its channel
+// down the rows with the taps' window in registers, so that each input and each weight is read once per tile instead
+// of once per row (one CTA per row re-reads the K-1 earlier rows and all weights from L2). The window is refilled from
+// the rows before the tile, or from the carried state, wherever a sequence starts or the rows are not consecutive.
+constexpr int kConvRows = 16, kConvMaxTaps = 8;
+
+template <typename XT>
+__global__ void __launch_bounds__(256)
+conv_dt_tile_kernel(const float* __restrict__ in, long long ld, int x_off, int dt_off, const XT* __restrict__ w,
+                    const XT* __restrict__ b, const XT* __restrict__ dt_bias, const XT* __restrict__ a_log,
+                    const float* __restrict__ conv_state, float* __restrict__ xbc, float* __restrict__ dt_out,
+                    float* __restrict__ decay_out, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
+                    const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int T, int C, int H, int K) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t0 = blockIdx.x * kConvRows;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= C + H) return;
+    if (c >= C) {
+        const int hh = c - C;
+        const float bias = ldf(dt_bias, hh), rate = expf(ldf(a_log, hh));
+        for (int r = 0; r < kConvRows && t0 + r < T; ++r) {
+            const long long t = t0 + r;
+            if (tok_seq[t] < 0) continue;
+            const float z = in[t * ld + dt_off + hh] + bias;
+            const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+            dt_out[t * H + hh] = dt;
+            decay_out[t * H + hh] = expf(-rate * dt);
+        }
+        return;
+    }
+    float raw[kConvRows];
+#pragma unroll
+    for (int r = 0; r < kConvRows; ++r) raw[r] = (t0 + r < T) ? in[static_cast<long long>(t0 + r) * ld + x_off + c] : 0.f;
+    float wt[kConvMaxTaps], win[kConvMaxTaps - 1];
+#pragma unroll
+    for (int j = 0; j < kConvMaxTaps; ++j) wt[j] = j < K ? ldf(w, static_cast<long long>(c) * K + j) : 0.f;
+    const float bias = ldf(b, c);
+    int prev_s = -1, prev_i = -2;
+#pragma unroll
+    for (int r = 0; r < kConvRows; ++r) {
+        const long long t = t0 + r;
+        if (t >= T) break;
+        const int s = tok_seq[t];
+        if (s < 0) continue;
+        const int i = static_cast<int>(t) - seq_start[s];
+        if (s != prev_s || i != prev_i + 1) {
+            const int pos0 = seq_pos0[s];
+            const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
+#pragma unroll
+            for (int j = 0; j < kConvMaxTaps - 1; ++j) {
+                const int rel = i - (K - 1) + j;   // row of the sequence's portion that tap j reads (negative: before it)
+                float x = 0.f;
+                if (j < K - 1) {
+                    if (rel >= 0)
+                        x = in[(t - i + rel) * ld + x_off + c];
+                    else if (pos0 + rel >= 0)
+                        x = st[static_cast<long long>(K - 1 + rel) * C + c];
+                }
+                win[j] = x;
+            }
+        }
+        float acc = bias;
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; ++j)
+            if (j < K - 1) acc = fmaf(wt[j], win[j], acc);
+        float wl = 0.f;
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps; ++j)
+            if (j == K - 1) wl = wt[j];
+        acc = fmaf(wl, raw[r], acc);
+        xbc[t * C + c] = silu_f(acc);
+        // slide: the window's entries 0 .. K-2 hold the K-1 inputs before the next row
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 2; ++j)
+            if (j < K - 2) win[j] = win[j + 1];
+#pragma unroll
+        for (int j = 0; j < kConvMaxTaps - 1; ++j)
+            if (j == K - 2) win[j] = raw[r];
+        prev_s = s;
+        prev_i = i;
+    }
+}
+
 // The carried window after the step: the raw inputs of the sequence's last K-1 positions. One thread per channel walks
 // the window front to back, so that a step shorter than the window shifts it in place.
 __global__ void __launch_bounds__(256)
@@ -526,6 +610,15 @@ int atx_conv_dt(const float* in, long long ld, int x_off, int dt_off, const void
     cfg.blockDim = dim3(256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
+    if (T >= 256 && K >= 2 && K <= kConvMaxTaps) {
+        cfg.gridDim = dim3((T + kConvRows - 1) / kConvRows, (C + H + 255) / 256);
+        ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
+                                   &cfg, conv_dt_tile_kernel<XT>, in, ld, x_off, dt_off, reinterpret_cast<const XT*>(w),
+                                   reinterpret_cast<const XT*>(b), reinterpret_cast<const XT*>(dt_bias),
+                                   reinterpret_cast<const XT*>(a_log), conv_state, xbc, dt_out, decay_out, tok_seq,
+                                   seq_start, seq_pos0, seq_slot, T, C, H, K)));
+        return ATX_OK;
+    }
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
                                &cfg, conv_dt_kernel<XT>, in, ld, x_off, dt_off, reinterpret_cast<const XT*>(w),
                                reinterpret_cast<const XT*>(b), reinterpret_cast<const XT*>(dt_bias),

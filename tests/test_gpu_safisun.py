@@ -67,13 +67,18 @@ def tokens(n, vocab=96, seed=0):
     return [int(t) for t in torch.randint(0, vocab, (n,), generator=torch.Generator().manual_seed(seed))]
 
 
-def rel(got, want):
-    """Worst row of rms(got - want) / rms(want), both with the row mean taken off."""
+def rel_rows(got, want):
+    """Per row: rms(got - want) / rms(want), both with the row mean taken off."""
     got, want = torch.as_tensor(got, dtype=F64), torch.as_tensor(want, dtype=F64)
     d = got - want
     d = d - d.mean(-1, keepdim=True)
     w = want - want.mean(-1, keepdim=True)
-    return float((d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt()).max())
+    return d.pow(2).mean(-1).sqrt() / w.pow(2).mean(-1).sqrt()
+
+
+def rel(got, want):
+    """Worst row of rel_rows."""
+    return float(rel_rows(got, want).max())
 
 
 TOL = {"float32": 2e-5, "bfloat16": 0.15}      # bf16: operand rounding through up to seven layer runs; fp32 is the sharp test
@@ -178,6 +183,56 @@ def test_mixed_batches_equal_each_request_alone():
     assert at == {k: len(v) for k, v in reqs.items()}
     for k in reqs:
         assert rel(np.concatenate(got[k]), want[k]) < TOL["float32"], k
+    assert eng.allocator.num_free == eng.allocator.num_blocks and eng.state_slots.num_free == 4
+
+
+def tensor_core_sized_model():
+    """Key sizes the chunked tensor-core recurrence (32 / 64) and the tensor-core attention (64) accept, so that bf16
+    prompt portions take those kernels and single tokens the token-by-token ones, on the same pages and state slots."""
+    ff = {"ff": 96, "kind": "dense"}
+    return model_cfg([mamba_layer(heads=4, vdim=16, state=64, groups=2, norm_groups=2, conv=4, mlp=ff),
+                      parallel_layer(mlp=ff, size=24, rot_dims=16, dim=64, vdim=64, heads=4, kv=2),
+                      lightning_layer(heads=3, dim=32, vdim=24)], width=128, loop={"start": 0, "stop": 2, "times": 2})
+
+
+def test_bf16_portions_on_the_tensor_cores_beside_single_tokens():
+    """Mixed steps in bf16 where prompt portions run on the chunked recurrence and the tensor-core attention while the
+    single tokens beside them run token by token: the per-sequence lists handed to the two kernel families start at
+    different offsets of the same step. Portions cross the 64-token chunk of the recurrence and the 24-token block of
+    the mask; each request is compared with the float64 reference and with itself run alone."""
+    cfg = tensor_core_sized_model()
+    wt = R.random_checkpoint(cfg, 15)
+    reqs = {"a": tokens(150, seed=1), "b": tokens(90, seed=2), "c": tokens(70, seed=3), "d": tokens(6, seed=5)}
+    want = {k: R.forward(cfg, wt, v) for k, v in reqs.items()}
+    steps = [[("a", 70), ("b", 2)], [("a", 1), ("b", 65)], [("a", 1), ("b", 1), ("c", 63)], [("a", 64), ("b", 1), ("c", 1),
+             ("d", 6)], [("b", 21), ("c", 2), ("a", 1)], [("a", 13), ("c", 4)]]
+    eng = engine(cfg, wt, "bfloat16", max_num_seqs=4, max_model_len=160, max_num_batched_tokens=512)
+    lib, _ = _lib()
+    assert lib.atx_linear_recurrence_chunked_supported(64) and lib.atx_attn_local_prefill_supported(64, 64, 0)
+    at = {k: 0 for k in reqs}
+    got = {k: [] for k in reqs}
+    for step in steps:
+        entries, end = [], []
+        for k, n in step:
+            entries.append((k, reqs[k][at[k]:at[k] + n], list(range(n))))
+            at[k] += n
+            if at[k] == len(reqs[k]):
+                end.append(k)
+        out = eng.feed(entries, end)
+        o = 0
+        for k, n in step:
+            got[k].append(out[o:o + n])
+            o += n
+    assert at == {k: len(v) for k, v in reqs.items()}
+    # A looped model with a norm after every sublayer has rows that magnify bf16 rounding several times over (the
+    # float64 reference itself moves by 0.3 on some rows when its weights get bf16-sized noise), so rows are judged
+    # together: a wrong offset, slot or page spoils whole requests, not one row in twenty.
+    for k in reqs:
+        mixed = np.concatenate(got[k])
+        alone = whole(eng, k + "-alone", reqs[k])
+        for other in (want[k], alone):
+            r = rel_rows(mixed, other)
+            assert float(r.median()) < 0.04 and float(r.quantile(0.9)) < 0.15 and float(r.max()) < 0.6, (k, r.max())
     assert eng.allocator.num_free == eng.allocator.num_blocks and eng.state_slots.num_free == 4
 
 
@@ -513,6 +568,55 @@ def test_short_convolution_carries_its_window_across_short_steps():
     assert at == n
     assert torch.allclose(torch.cat(outs), want, atol=1e-5)
     assert torch.allclose(torch.cat(dts), want_dt, atol=1e-5) and torch.allclose(torch.cat(decs), want_dec, atol=1e-5)
+
+
+@pytest.mark.parametrize("K", [2, 4, 7])
+def test_short_convolution_on_prompt_sized_steps_with_several_sequences(K):
+    """Steps of 256 rows and more take the row-tiled kernel: three sequences of uneven length in one step (starting in
+    the middle of a tile of rows, one of them shorter than the window), padded rows between them, and a second step
+    that continues two of them from the carried window."""
+    lib, cabi = _lib()
+    Cc, H = 300, 5
+    g = torch.Generator().manual_seed(33)
+    lens = [131, K - 1 if K > 2 else 1, 210]
+    x = [torch.randn(n + 140, Cc + H, generator=g, dtype=F64) for n in lens]
+    taps, bias = torch.randn(Cc, K, generator=g, dtype=F64), torch.randn(Cc, generator=g, dtype=F64)
+    dt_bias, a_log = torch.randn(H, generator=g, dtype=F64), torch.randn(H, generator=g, dtype=F64)
+    want = [R.swish(R.causal_taps(xi[:, :Cc], taps, bias)) for xi in x]
+    f = lambda t: t.float().to(DEV).contiguous()
+    taps_d, bias_d, dtb_d, al_d = f(taps), f(bias), f(dt_bias), f(a_log)
+    state = torch.full((4, K - 1, Cc), 1e30, device=DEV)
+    slots = [2, 0, 3]
+
+    def step(parts):           # parts: (sequence, first position, rows); three padded rows after every sequence
+        rows, seq_of, starts = [], [], []
+        for si, (q, p0, n) in enumerate(parts):
+            starts.append(len(seq_of))
+            rows.append(x[q][p0:p0 + n])
+            rows.append(torch.full((3, Cc + H), float("nan"), dtype=F64))
+            seq_of += [si] * n + [-1] * 3
+        xd = f(torch.cat(rows))
+        T = xd.shape[0]
+        assert T >= 256
+        out, dto, deco = (torch.zeros(T, w_, device=DEV) for w_ in (Cc, H, H))
+        s0, sc = _i32(starts), _i32([n for _, _, n in parts])
+        sp, ss, ts = _i32([p0 for _, p0, _ in parts]), _i32([slots[q] for q, _, _ in parts]), _i32(seq_of)
+        rc = lib.atx_conv_dt(xd.data_ptr(), Cc + H, 0, Cc, taps_d.data_ptr(), bias_d.data_ptr(), dtb_d.data_ptr(),
+                             al_d.data_ptr(), state.data_ptr(), out.data_ptr(), dto.data_ptr(), deco.data_ptr(),
+                             ts.data_ptr(), s0.data_ptr(), sp.data_ptr(), ss.data_ptr(), T, Cc, H, K, cabi.DT_F32, 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        rc = lib.atx_conv_state_update(xd.data_ptr(), Cc + H, 0, state.data_ptr(), s0.data_ptr(), sc.data_ptr(),
+                                       sp.data_ptr(), ss.data_ptr(), len(parts), Cc, K, 0, _st())
+        assert rc == 0
+        torch.cuda.synchronize()
+        for (q, p0, n), a in zip(parts, starts):
+            assert torch.allclose(out[a:a + n].cpu().double(), want[q][p0:p0 + n], atol=1e-5), (q, p0)
+            dt_want = torch.log1p(torch.exp(x[q][p0:p0 + n, Cc:] + dt_bias))
+            assert torch.allclose(dto[a:a + n].cpu().double(), dt_want, atol=1e-5)
+            assert torch.allclose(deco[a:a + n].cpu().double(), torch.exp(-torch.exp(a_log) * dt_want), atol=1e-5)
+
+    step([(0, 0, lens[0]), (1, 0, lens[1]), (2, 0, lens[2])])
+    step([(2, lens[2], 140), (1, lens[1], 1), (0, lens[0], 140)])
 
 
 def test_fma_gemm_and_norm_kernels_match_their_formulas():
