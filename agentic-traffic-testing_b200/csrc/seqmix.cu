@@ -232,13 +232,16 @@ conv_dt_kernel(const float* __restrict__ in, long long ld, int x_off, int dt_off
 // the rows before the tile, or from the carried state, wherever a sequence starts or the rows are not consecutive.
 constexpr int kConvRows = 16, kConvMaxTaps = 8;
 
-template <typename XT>
+// KT: the number of taps when it is one of the common ones (loops and window fold at compile time), 0: read K.
+template <typename XT, int KT>
 __global__ void __launch_bounds__(256)
 conv_dt_tile_kernel(const float* __restrict__ in, long long ld, int x_off, int dt_off, const XT* __restrict__ w,
                     const XT* __restrict__ b, const XT* __restrict__ dt_bias, const XT* __restrict__ a_log,
                     const float* __restrict__ conv_state, float* __restrict__ xbc, float* __restrict__ dt_out,
                     float* __restrict__ decay_out, const int* __restrict__ tok_seq, const int* __restrict__ seq_start,
-                    const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int T, int C, int H, int K) {
+                    const int* __restrict__ seq_pos0, const int* __restrict__ seq_slot, int T, int C, int H, int K_rt) {
+    constexpr int MT = KT ? KT : kConvMaxTaps;   // registers for taps and window
+    const int K = KT ? KT : K_rt;
     pdl_launch_dependents();
     pdl_wait();
     const int t0 = blockIdx.x * kConvRows;
@@ -260,9 +263,9 @@ conv_dt_tile_kernel(const float* __restrict__ in, long long ld, int x_off, int d
     float raw[kConvRows];
 #pragma unroll
     for (int r = 0; r < kConvRows; ++r) raw[r] = (t0 + r < T) ? in[static_cast<long long>(t0 + r) * ld + x_off + c] : 0.f;
-    float wt[kConvMaxTaps], win[kConvMaxTaps - 1];
+    float wt[MT], win[MT > 1 ? MT - 1 : 1];
 #pragma unroll
-    for (int j = 0; j < kConvMaxTaps; ++j) wt[j] = j < K ? ldf(w, static_cast<long long>(c) * K + j) : 0.f;
+    for (int j = 0; j < MT; ++j) wt[j] = j < K ? ldf(w, static_cast<long long>(c) * K + j) : 0.f;
     const float bias = ldf(b, c);
     int prev_s = -1, prev_i = -2;
 #pragma unroll
@@ -276,7 +279,7 @@ conv_dt_tile_kernel(const float* __restrict__ in, long long ld, int x_off, int d
             const int pos0 = seq_pos0[s];
             const float* st = conv_state + static_cast<long long>(seq_slot[s]) * (K - 1) * C;
 #pragma unroll
-            for (int j = 0; j < kConvMaxTaps - 1; ++j) {
+            for (int j = 0; j < MT - 1; ++j) {
                 const int rel = i - (K - 1) + j;   // row of the sequence's portion that tap j reads (negative: before it)
                 float x = 0.f;
                 if (j < K - 1) {
@@ -290,20 +293,21 @@ conv_dt_tile_kernel(const float* __restrict__ in, long long ld, int x_off, int d
         }
         float acc = bias;
 #pragma unroll
-        for (int j = 0; j < kConvMaxTaps - 1; ++j)
+        for (int j = 0; j < MT - 1; ++j)
             if (j < K - 1) acc = fmaf(wt[j], win[j], acc);
         float wl = 0.f;
 #pragma unroll
-        for (int j = 0; j < kConvMaxTaps; ++j)
+        for (int j = 0; j < MT; ++j)
             if (j == K - 1) wl = wt[j];
         acc = fmaf(wl, raw[r], acc);
-        xbc[t * C + c] = silu_f(acc);
+        // bf16 models: the activation of a short convolution may be bf16-accurate, so the fast exponential and division
+        xbc[t * C + c] = sizeof(XT) == 2 ? __fdividef(acc, 1.f + __expf(-acc)) : silu_f(acc);
         // slide: the window's entries 0 .. K-2 hold the K-1 inputs before the next row
 #pragma unroll
-        for (int j = 0; j < kConvMaxTaps - 2; ++j)
+        for (int j = 0; j < MT - 2; ++j)
             if (j < K - 2) win[j] = win[j + 1];
 #pragma unroll
-        for (int j = 0; j < kConvMaxTaps - 1; ++j)
+        for (int j = 0; j < MT - 1; ++j)
             if (j == K - 2) win[j] = raw[r];
         prev_s = s;
         prev_i = i;
@@ -612,11 +616,21 @@ int atx_conv_dt(const float* in, long long ld, int x_off, int dt_off, const void
     set_pdl2(cfg, attr, flags);
     if (T >= 256 && K >= 2 && K <= kConvMaxTaps) {
         cfg.gridDim = dim3((T + kConvRows - 1) / kConvRows, (C + H + 255) / 256);
-        ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
-                                   &cfg, conv_dt_tile_kernel<XT>, in, ld, x_off, dt_off, reinterpret_cast<const XT*>(w),
-                                   reinterpret_cast<const XT*>(b), reinterpret_cast<const XT*>(dt_bias),
-                                   reinterpret_cast<const XT*>(a_log), conv_state, xbc, dt_out, decay_out, tok_seq,
-                                   seq_start, seq_pos0, seq_slot, T, C, H, K)));
+#define ATX_CONV_TILE(KT_)                                                                                                \
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(                                                                   \
+                               &cfg, conv_dt_tile_kernel<XT, KT_>, in, ld, x_off, dt_off, reinterpret_cast<const XT*>(w), \
+                               reinterpret_cast<const XT*>(b), reinterpret_cast<const XT*>(dt_bias),                      \
+                               reinterpret_cast<const XT*>(a_log), conv_state, xbc, dt_out, decay_out, tok_seq,           \
+                               seq_start, seq_pos0, seq_slot, T, C, H, K)))
+        if (K == 4)
+            ATX_CONV_TILE(4);
+        else if (K == 3)
+            ATX_CONV_TILE(3);
+        else if (K == 2)
+            ATX_CONV_TILE(2);
+        else
+            ATX_CONV_TILE(0);
+#undef ATX_CONV_TILE
         return ATX_OK;
     }
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
