@@ -194,8 +194,15 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
 // One CTA = 64 consecutive rows of one sequence's portion x one query head; a warp owns 16 rows. Key tiles of 64
 // positions are gathered from the pages into shared memory; S = Q K^T and O += P V run on mma.sync m16n8k16 (bf16 in,
 // fp32 accumulate), everything between (scale, tanh cap, block-local causal mask, running maximum and sum with the
-// zero-score sink, rescale of O) is fp32 in registers. The portion's sequences are listed as (first row, rows, first
-// position); a CTA finds its tile by walking that list.
+// zero-score sink, rescale of O) is fp32 in registers. Key/value tiles arrive by cp.async into two stages, the next
+// tile in flight while the current one is multiplied; the query tile is staged in the second stage's space before the
+// pipeline starts (its fragments then live in registers), which keeps a CTA at four tiles of shared memory and three
+// CTAs on an SM. The portion's sequences are listed as (first row, rows, first position); a CTA finds its tile by
+// walking that list.
+__device__ __forceinline__ void cp_async16_zfill(void* smem_dst, const void* gsrc, bool valid) {
+    const uint32_t sz = valid ? 16u : 0u;   // source size 0: sixteen bytes of zeros, nothing is read
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(sz) : "memory");
+}
 __device__ __forceinline__ float tanh_via_exp(float x) {
     const float t = __expf(2.f * x);          // inf for large x: 2 / inf = 0 -> 1; 0 for very negative x -> -1
     return 1.f - __fdividef(2.f, t + 1.f);
@@ -213,9 +220,10 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      int chunk, int sink, float out_scale) {
     constexpr int LQ = D + 8, LV = VD + 8;     // padded rows: ldmatrix without bank conflicts, 16-byte aligned
     extern __shared__ __align__(16) unsigned char smem_raw[];
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    __nv_bfloat16* sK = sQ + kTcRows * LQ;
-    __nv_bfloat16* sV = sK + kTcKeys * LQ;
+    static_assert(kTcRows == kTcKeys, "the query tile is staged in a key stage");
+    __nv_bfloat16* sKs = reinterpret_cast<__nv_bfloat16*>(smem_raw);   // [2][kTcKeys][LQ]
+    __nv_bfloat16* sVs = sKs + 2 * kTcKeys * LQ;                        // [2][kTcKeys][LV]
+    __nv_bfloat16* sQ = sKs + kTcKeys * LQ;                             // = key stage 1, until the pipeline starts
     pdl_launch_dependents();
     pdl_wait();
     int tile = blockIdx.x, s = 0;
@@ -258,30 +266,38 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     plo[1] = chunk > 0 ? (pr[1] / chunk) * chunk : 0;
     const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
 
-    for (int k0 = lo; k0 <= p1; k0 += kTcKeys) {
-        __syncthreads();   // the previous tile has been consumed
+    __syncthreads();   // every warp holds its query fragments: key stage 1 may be filled
+    auto load_tile = [&](int k0, int stage) {
+        __nv_bfloat16* dk = sKs + stage * kTcKeys * LQ;
+        __nv_bfloat16* dv = sVs + stage * kTcKeys * LV;
         for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
             const int r = c / (D / 8), part = c - r * (D / 8);
-            const int kp = k0 + r;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (kp <= p1) {
-                const long long slot = (static_cast<long long>(bt[kp / bs]) * G + g) * bs + (kp % bs);
-                v = __ldg(reinterpret_cast<const uint4*>(k_cache + slot * D + part * 8));
-            }
-            *reinterpret_cast<uint4*>(sK + r * LQ + part * 8) = v;
+            const int kp = k0 + r, kq = min(kp, p1);   // rows past the portion become zeros (0 x garbage would not be 0)
+            const long long slot = (static_cast<long long>(bt[kq / bs]) * G + g) * bs + (kq % bs);
+            cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot * D + part * 8, kp <= p1);
         }
         for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
             const int r = c / (VD / 8), part = c - r * (VD / 8);
-            const int kp = k0 + r;
-            uint4 v = make_uint4(0, 0, 0, 0);   // rows past the portion stay zero: 0 x garbage would not be 0
-            if (kp <= p1) {
-                const long long slot = (static_cast<long long>(bt[kp / bs]) * G + g) * bs + (kp % bs);
-                v = __ldg(reinterpret_cast<const uint4*>(v_cache + slot * VD + part * 8));
-            }
-            *reinterpret_cast<uint4*>(sV + r * LV + part * 8) = v;
+            const int kp = k0 + r, kq = min(kp, p1);
+            const long long slot = (static_cast<long long>(bt[kq / bs]) * G + g) * bs + (kq % bs);
+            cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot * VD + part * 8, kp <= p1);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int n_tiles = (p1 - lo) / kTcKeys + 1;
+    load_tile(lo, 0);
+    for (int it = 0; it < n_tiles; ++it) {
+        const int k0 = lo + it * kTcKeys;
+        if (it + 1 < n_tiles) {
+            load_tile(k0 + kTcKeys, (it + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        if (k0 > p0 + warp * 16 + 15) continue;   // every key of the tile lies after this warp's rows (warp-uniform)
+        const __nv_bfloat16* sK = sKs + (it & 1) * kTcKeys * LQ;
+        const __nv_bfloat16* sV = sVs + (it & 1) * kTcKeys * LV;
+        if (k0 <= p0 + warp * 16 + 15) {   // else every key of the tile lies after this warp's rows (warp-uniform)
         float sc[kTcKeys / 8][4];
 #pragma unroll
         for (int i = 0; i < kTcKeys / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
@@ -358,6 +374,8 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                 mma_bf16(o[2 * nb2 + 1], a, b2, b3);
             }
         }
+        }
+        __syncthreads();   // the stage is free for the tile after the next
     }
 #pragma unroll
     for (int rr = 0; rr < 2; ++rr) {
@@ -378,7 +396,7 @@ static int launch_attn_tc(const void* q, const void* k_cache, const void* v_cach
                           int max_tiles, const float* gate, long long ldg, void* out, long long ldo, int H, int G, int bs,
                           float scale, float softcap, int chunk, int sink, float out_scale, int flags,
                           cudaStream_t stream) {
-    const int smem = (kTcRows + kTcKeys) * (D + 8) * 2 + kTcKeys * (VD + 8) * 2;
+    const int smem = 2 * kTcKeys * (D + 8) * 2 + 2 * kTcKeys * (VD + 8) * 2;
     static bool attr_done = false;
     if (!attr_done && smem > 48 * 1024) {
         ATX_CUDA(cudaFuncSetAttribute(attn_local_tc_kernel<D, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
