@@ -29,6 +29,17 @@ __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p, long
 __device__ __forceinline__ void stf(float* p, long long i, float v) { p[i] = v; }
 __device__ __forceinline__ void stf(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
 
+// four consecutive elements at element index 4 * i4 (16-byte / 8-byte aligned by the caller's choice of the vector path)
+__device__ __forceinline__ float4 ld4(const float* p, long long i4) { return reinterpret_cast<const float4*>(p)[i4]; }
+__device__ __forceinline__ float4 ld4(const __nv_bfloat16* p, long long i4) {
+    const uint2 u = reinterpret_cast<const uint2*>(p)[i4];
+    return make_float4(bf16lo(u.x), bf16hi(u.x), bf16lo(u.y), bf16hi(u.y));
+}
+__device__ __forceinline__ void st4(float* p, long long i4, float4 v) { reinterpret_cast<float4*>(p)[i4] = v; }
+__device__ __forceinline__ void st4(__nv_bfloat16* p, long long i4, float4 v) {
+    reinterpret_cast<uint2*>(p)[i4] = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+}
+
 __device__ __forceinline__ float silu_f(float x) { return x / (1.f + expf(-x)); }
 __device__ __forceinline__ float sigmoid_f(float x) { return 1.f / (1.f + expf(-x)); }
 
@@ -88,13 +99,13 @@ __global__ void __launch_bounds__(128) concat_embed_kernel(const float* __restri
 // With `rows` the residual itself is left untouched (the gathered rows feed the LM head only).
 // zero_y: the row of y is cleared once it has been read, so that the next split-K GEMM can accumulate into it;
 // CTAs beyond T clear zero_ptr (the accumulator of the GEMM that consumes `out`).
-template <typename XT>
+template <typename XT, bool VEC>
 __global__ void __launch_bounds__(1024)
 resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __restrict__ w_post,
                   const XT* __restrict__ vec, const XT* __restrict__ w_pre, XT* __restrict__ out,
                   const int* __restrict__ rows, int T, int W, float eps, int zero_y, uint4* __restrict__ zero_ptr,
                   long long zero_vecs) {
-    extern __shared__ float srow[];
+    extern __shared__ __align__(16) float srow[];
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -109,6 +120,43 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
     const long long r = rows ? rows[t] : t;
     float* hr = h + r * W;
     float rs_y = 0.f;
+    if (VEC) {   // W a multiple of 4 and every row 16-byte aligned (8 for bf16): four elements per load and store
+        const int W4 = W / 4;
+        float4* srow4 = reinterpret_cast<float4*>(srow);
+        if (y) {
+            float ss = 0.f;
+            for (int i = threadIdx.x; i < W4; i += blockDim.x) {
+                const float4 v = ld4(y + r * W, i);
+                if (zero_y) st4(y + r * W, i, make_float4(0.f, 0.f, 0.f, 0.f));
+                srow4[i] = v;
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            rs_y = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
+        }
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < W4; i += blockDim.x) {
+            float4 v = ld4(hr, i);
+            if (y) {
+                const float4 a = srow4[i], wp = ld4(w_post, i);
+                v.x += a.x * rs_y * wp.x, v.y += a.y * rs_y * wp.y, v.z += a.z * rs_y * wp.z, v.w += a.w * rs_y * wp.w;
+            }
+            if (vec) {
+                const float4 b = ld4(vec, i);
+                v.x += b.x, v.y += b.y, v.z += b.z, v.w += b.w;
+            }
+            if ((y || vec) && !rows) st4(hr, i, v);
+            srow4[i] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        if (!w_pre) return;
+        const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(W) + eps);
+        XT* o = out + static_cast<long long>(t) * W;
+        for (int i = threadIdx.x; i < W4; i += blockDim.x) {
+            const float4 a = srow4[i], wq = ld4(w_pre, i);
+            st4(o, i, make_float4(a.x * rs * wq.x, a.y * rs * wq.y, a.z * rs * wq.z, a.w * rs * wq.w));
+        }
+        return;
+    }
     if (y) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < W; i += blockDim.x) {
@@ -153,11 +201,12 @@ __global__ void __launch_bounds__(256) gated_act_kernel(const float* __restrict_
 // mode 0: out = rms(y) * w * sigmoid(g) * scale      (gate after the norm)
 // mode 1: u = y * silu(g); out = rms(u) * w * scale  (gate before the norm)
 // The norm runs over n / groups consecutive elements; grid (T, groups).
-template <typename XT>
+template <typename XT, bool VEC>
 __global__ void __launch_bounds__(1024)
 gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __restrict__ gate, long long ldg,
                   const XT* __restrict__ w, XT* __restrict__ out, long long ldo, int n_group, float eps, int mode,
                   float scale) {
+    extern __shared__ __align__(16) float sgn[];   // VEC: the group's gated values between the two passes
     __shared__ float red[32];
     pdl_launch_dependents();
     pdl_wait();
@@ -165,6 +214,33 @@ gated_norm_kernel(const float* __restrict__ y, long long ldy, const float* __res
     const int c0 = blockIdx.y * n_group;
     const float* yr = y + t * ldy + c0;
     const float* gr = gate + t * ldg + c0;
+    if (VEC) {   // sizes and pitches multiples of 4, pointers 16-byte aligned: four elements per access, one gate pass
+        const int n4 = n_group / 4;
+        float4* s4 = reinterpret_cast<float4*>(sgn);
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            float4 v = ld4(yr, i);
+            if (mode == 1) {
+                const float4 g = ld4(gr, i);
+                v.x *= silu_f(g.x), v.y *= silu_f(g.y), v.z *= silu_f(g.z), v.w *= silu_f(g.w);
+            }
+            s4[i] = v;
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+        const float rs = rsqrtf(block_sum(ss, red) / static_cast<float>(n_group) + eps) * scale;
+        XT* o = out + t * ldo + c0;
+        for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+            float4 v = s4[i];
+            const float4 ww = ld4(w + c0, i);
+            v.x *= rs * ww.x, v.y *= rs * ww.y, v.z *= rs * ww.z, v.w *= rs * ww.w;
+            if (mode == 0) {
+                const float4 g = ld4(gr, i);
+                v.x *= sigmoid_f(g.x), v.y *= sigmoid_f(g.y), v.z *= sigmoid_f(g.z), v.w *= sigmoid_f(g.w);
+            }
+            st4(o, i, v);
+        }
+        return;
+    }
     float ss = 0.f;
     for (int i = threadIdx.x; i < n_group; i += blockDim.x) {
         float v = yr[i];
@@ -556,11 +632,19 @@ int atx_resid_norm(float* h, float* y, const void* w_post, const void* vec, cons
     cfg.dynamicSmemBytes = static_cast<size_t>(W) * 4;
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
-    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(
-                               &cfg, resid_norm_kernel<XT>, h, y, reinterpret_cast<const XT*>(w_post),
-                               reinterpret_cast<const XT*>(vec), reinterpret_cast<const XT*>(w_pre),
-                               reinterpret_cast<XT*>(out), rows, T, W, eps, zero_y, reinterpret_cast<uint4*>(zero_ptr),
-                               zv)));
+    auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const bool v4 = W % 4 == 0 && al16(h) && al16(y) && al16(w_post) && al16(vec) && al16(w_pre) && al16(out);
+#define ATX_RESID(VEC_)                                                                                                   \
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(                                                                   \
+                               &cfg, resid_norm_kernel<XT, VEC_>, h, y, reinterpret_cast<const XT*>(w_post),              \
+                               reinterpret_cast<const XT*>(vec), reinterpret_cast<const XT*>(w_pre),                      \
+                               reinterpret_cast<XT*>(out), rows, T, W, eps, zero_y, reinterpret_cast<uint4*>(zero_ptr),   \
+                               zv)))
+    if (v4)
+        ATX_RESID(true);
+    else
+        ATX_RESID(false);
+#undef ATX_RESID
     return ATX_OK;
 }
 
@@ -593,9 +677,25 @@ int atx_gated_norm(const float* y, long long ldy, const float* gate, long long l
     cfg.blockDim = dim3(T <= 512 && n / groups >= 2048 ? 1024 : 256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
-    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_kernel<XT>, y, ldy, gate, ldg,
-                                                       reinterpret_cast<const XT*>(w), reinterpret_cast<XT*>(out), ldo,
-                                                       n / groups, eps, mode, scale)));
+    auto al16 = [](const void* p) { return reinterpret_cast<uintptr_t>(p) % 16 == 0; };
+    const int ng = n / groups;
+    const bool v4 = ng % 4 == 0 && ldy % 4 == 0 && ldg % 4 == 0 && ldo % 4 == 0 && al16(y) && al16(gate) && al16(w) &&
+                    al16(out) && ng * 4 <= 96 * 1024;
+#define ATX_GNORM(VEC_)                                                                                                  \
+    ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, gated_norm_kernel<XT, VEC_>, y, ldy, gate, ldg,             \
+                                                       reinterpret_cast<const XT*>(w), reinterpret_cast<XT*>(out), ldo,  \
+                                                       ng, eps, mode, scale)))
+    if (v4) {
+        cfg.dynamicSmemBytes = static_cast<size_t>(ng) * 4;
+        if (ng * 4 > 48 * 1024) {
+            ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaFuncSetAttribute(gated_norm_kernel<XT, true>,
+                                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024)));
+        }
+        ATX_GNORM(true);
+    } else {
+        ATX_GNORM(false);
+    }
+#undef ATX_GNORM
     return ATX_OK;
 }
 

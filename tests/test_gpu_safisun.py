@@ -631,25 +631,25 @@ def test_fma_gemm_and_norm_kernels_match_their_formulas():
         assert rc == 0, lib.atx_last_error()
         assert torch.allclose(out[:, :N].cpu().double(), x.cpu().double() @ w.cpu().double().T, atol=1e-4, rtol=tol)
         assert float(out[:, N:].abs().max()) == 0.0
-    W = 70
-    h, y = torch.randn(T, W, generator=g, dtype=F64), 3.0 * torch.randn(T, W, generator=g, dtype=F64)
-    wp, vec, wn = (torch.randn(W, generator=g, dtype=F64) for _ in range(3))
-    hd, o = h.float().to(DEV), torch.zeros(T, W, device=DEV)
-    f = lambda t: t.float().to(DEV).contiguous()
-    yd, wpd, vecd, wnd = f(y), f(wp), f(vec), f(wn)
-    rc = lib.atx_resid_norm(hd.data_ptr(), yd.data_ptr(), wpd.data_ptr(), vecd.data_ptr(), wnd.data_ptr(),
-                            o.data_ptr(), None, T, W, 1e-5, 1, None, 0, cabi.DT_F32, 0, _st())
-    assert rc == 0, lib.atx_last_error()
-    h2 = h + R.unit_rms(y, 1e-5) * wp + vec
-    assert float(yd.abs().max()) == 0.0        # the sublayer output is handed back cleared
-    assert torch.allclose(hd.cpu().double(), h2, atol=1e-5) and torch.allclose(o.cpu().double(), R.unit_rms(h2, 1e-5) * wn, atol=1e-5)
-    n, groups = 60, 3
-    yy, gg, ww = torch.randn(T, n, generator=g, dtype=F64), torch.randn(T, n, generator=g, dtype=F64), torch.randn(n, generator=g, dtype=F64)
-    for mode, want in ((0, R.unit_rms(yy, 1e-5) * ww * torch.sigmoid(gg) * 0.7),
-                       (1, R.unit_rms((yy * R.swish(gg)).view(T, groups, n // groups), 1e-5).reshape(T, n) * ww * 0.7)):
-        o = torch.zeros(T, n, device=DEV)
-        yyd, ggd, wwd = f(yy), f(gg), f(ww)
-        rc = lib.atx_gated_norm(yyd.data_ptr(), n, ggd.data_ptr(), n, wwd.data_ptr(), o.data_ptr(), n, T, n,
-                                1 if mode == 0 else groups, 1e-5, mode, 0.7, cabi.DT_F32, 0, _st())
+    for W in (70, 72):            # 70: element-wise path; 72: four elements per access
+        h, y = torch.randn(T, W, generator=g, dtype=F64), 3.0 * torch.randn(T, W, generator=g, dtype=F64)
+        wp, vec, wn = (torch.randn(W, generator=g, dtype=F64) for _ in range(3))
+        hd, o = h.float().to(DEV), torch.zeros(T, W, device=DEV)
+        f = lambda t: t.float().to(DEV).contiguous()
+        yd, wpd, vecd, wnd = f(y), f(wp), f(vec), f(wn)
+        rc = lib.atx_resid_norm(hd.data_ptr(), yd.data_ptr(), wpd.data_ptr(), vecd.data_ptr(), wnd.data_ptr(),
+                                o.data_ptr(), None, T, W, 1e-5, 1, None, 0, cabi.DT_F32, 0, _st())
         assert rc == 0, lib.atx_last_error()
-        assert torch.allclose(o.cpu().double(), want, atol=1e-5), mode
+        h2 = h + R.unit_rms(y, 1e-5) * wp + vec
+        assert float(yd.abs().max()) == 0.0        # the sublayer output is handed back cleared
+        assert torch.allclose(hd.cpu().double(), h2, atol=1e-5) and torch.allclose(o.cpu().double(), R.unit_rms(h2, 1e-5) * wn, atol=1e-5)
+    for n, groups in ((60, 3), (66, 3)):      # groups of 20: four elements per access; of 22: element-wise
+        yy, gg, ww = torch.randn(T, n, generator=g, dtype=F64), torch.randn(T, n, generator=g, dtype=F64), torch.randn(n, generator=g, dtype=F64)
+        for mode, want in ((0, R.unit_rms(yy, 1e-5) * ww * torch.sigmoid(gg) * 0.7),
+                           (1, R.unit_rms((yy * R.swish(gg)).view(T, groups, n // groups), 1e-5).reshape(T, n) * ww * 0.7)):
+            o = torch.zeros(T, n, device=DEV)
+            yyd, ggd, wwd = f(yy), f(gg), f(ww)
+            rc = lib.atx_gated_norm(yyd.data_ptr(), n, ggd.data_ptr(), n, wwd.data_ptr(), o.data_ptr(), n, T, n,
+                                    1 if mode == 0 else groups, 1e-5, mode, 0.7, cabi.DT_F32, 0, _st())
+            assert rc == 0, lib.atx_last_error()
+            assert torch.allclose(o.cpu().double(), want, atol=1e-5), mode
