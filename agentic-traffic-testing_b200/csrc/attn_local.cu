@@ -207,11 +207,21 @@ __device__ __forceinline__ float tanh_via_exp(float x) {
     const float t = __expf(2.f * x);          // inf for large x: 2 / inf = 0 -> 1; 0 for very negative x -> -1
     return 1.f - __fdividef(2.f, t + 1.f);
 }
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float rcp_approx(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 
 constexpr int kTcRows = 64, kTcKeys = 64;
 
 template <int D, int VD>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (D <= 64 ? 4 : 3))
 attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                      const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
                      const int* __restrict__ seq_start, const int* __restrict__ seq_count,
@@ -226,7 +236,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     __nv_bfloat16* sQ = sKs + kTcKeys * LQ;                             // = key stage 1, until the pipeline starts
     pdl_launch_dependents();
     pdl_wait();
-    int tile = blockIdx.x, s = 0;
+    int tile = gridDim.x - 1 - blockIdx.x, s = 0;   // later tiles see more keys: the heaviest start first
     for (; s < n_seqs; ++s) {
         const int nt = (seq_count[s] + kTcRows - 1) / kTcRows;
         if (tile < nt) break;
@@ -264,23 +274,42 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     pr[1] = pr[0] + 8;
     plo[0] = chunk > 0 ? (pr[0] / chunk) * chunk : 0;
     plo[1] = chunk > 0 ? (pr[1] / chunk) * chunk : 0;
-    const float inv_cap = softcap > 0.f ? 1.f / softcap : 0.f;
+    // Scores live in the base-2 domain (s * log2 e), so that every exponential is one ex2. With a cap c:
+    // c tanh(x / c) = c - 2c / (1 + exp(2x / c)), one ex2 and one rcp; the constants carry scale and log2 e.
+    constexpr float kLog2e = 1.4426950408889634f;
+    const float c_in = softcap > 0.f ? 2.f * scale / softcap * kLog2e : scale * kLog2e;
+    const float cap2 = softcap * kLog2e;
+    const int plo_last = chunk > 0 ? ((p0 + warp * 16 + 15) / chunk) * chunk : 0;   // lower edge of this warp's last row
 
     __syncthreads();   // every warp holds its query fragments: key stage 1 may be filled
+    const int bs_shift = (bs & (bs - 1)) == 0 ? __ffs(bs) - 1 : -1;   // pages of 2^n tokens: shift and mask, no division
+    auto slot_of = [&](int kq) -> long long {
+        const int blk = bs_shift >= 0 ? kq >> bs_shift : kq / bs;
+        return (static_cast<long long>(bt[blk]) * G + g) * bs + (kq - blk * bs);
+    };
     auto load_tile = [&](int k0, int stage) {
         __nv_bfloat16* dk = sKs + stage * kTcKeys * LQ;
         __nv_bfloat16* dv = sVs + stage * kTcKeys * LV;
-        for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
-            const int r = c / (D / 8), part = c - r * (D / 8);
-            const int kp = k0 + r, kq = min(kp, p1);   // rows past the portion become zeros (0 x garbage would not be 0)
-            const long long slot = (static_cast<long long>(bt[kq / bs]) * G + g) * bs + (kq % bs);
-            cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot * D + part * 8, kp <= p1);
-        }
-        for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
-            const int r = c / (VD / 8), part = c - r * (VD / 8);
-            const int kp = k0 + r, kq = min(kp, p1);
-            const long long slot = (static_cast<long long>(bt[kq / bs]) * G + g) * bs + (kq % bs);
-            cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot * VD + part * 8, kp <= p1);
+        // rows past the portion become zeros (0 x garbage would not be 0)
+        if constexpr (D == VD) {   // one page lookup per row serves the key and the value
+            for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
+                const int r = c / (D / 8), part = c - r * (D / 8);
+                const int kp = k0 + r;
+                const long long slot = slot_of(min(kp, p1));
+                cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot * D + part * 8, kp <= p1);
+                cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot * VD + part * 8, kp <= p1);
+            }
+        } else {
+            for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
+                const int r = c / (D / 8), part = c - r * (D / 8);
+                const int kp = k0 + r;
+                cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot_of(min(kp, p1)) * D + part * 8, kp <= p1);
+            }
+            for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
+                const int r = c / (VD / 8), part = c - r * (VD / 8);
+                const int kp = k0 + r;
+                cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot_of(min(kp, p1)) * VD + part * 8, kp <= p1);
+            }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -313,18 +342,36 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             }
         }
         float mx[2] = {-INFINITY, -INFINITY};
+        // only tiles that reach past the warp's first row or start before its last row's block need the mask
+        const bool edge = k0 + kTcKeys - 1 > p0 + warp * 16 || k0 < plo_last;
+        if (softcap > 0.f) {
+#pragma unroll
+            for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e)
+                    sc[nb][e] = fmaf(-2.f * cap2, rcp_approx(1.f + ex2_approx(sc[nb][e] * c_in)), cap2);
+            }
+        } else {
+#pragma unroll
+            for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) sc[nb][e] *= c_in;
+            }
+        }
+        if (edge) {
+#pragma unroll
+            for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = k0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    if (col > pr[e >> 1] || col < plo[e >> 1]) sc[nb][e] = -INFINITY;
+                }
+            }
+        }
 #pragma unroll
         for (int nb = 0; nb < kTcKeys / 8; ++nb) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int col = k0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-                const int rr = e >> 1;
-                float v = sc[nb][e] * scale;
-                if (softcap > 0.f) v = softcap * tanh_via_exp(v * inv_cap);
-                if (col > pr[rr] || col < plo[rr]) v = -INFINITY;
-                sc[nb][e] = v;
-                mx[rr] = fmaxf(mx[rr], v);
-            }
+            for (int e = 0; e < 4; ++e) mx[e >> 1] = fmaxf(mx[e >> 1], sc[nb][e]);
         }
         float corr[2], rs[2] = {0.f, 0.f};
 #pragma unroll
@@ -332,15 +379,17 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 1));
             mx[rr] = fmaxf(mx[rr], __shfl_xor_sync(0xffffffffu, mx[rr], 2));
             const float mn = fmaxf(m[rr], mx[rr]);
-            corr[rr] = (m[rr] == -INFINITY) ? 0.f : __expf(m[rr] - mn);
+            corr[rr] = (m[rr] == -INFINITY) ? 0.f : ex2_approx(m[rr] - mn);
             m[rr] = mn;
         }
+        // a row that has seen no key yet (no sink, everything masked so far): exponent base 0, so that -inf - m is -inf, not NaN
+        const float mu[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
 #pragma unroll
         for (int nb = 0; nb < kTcKeys / 8; ++nb) {
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int rr = e >> 1;
-                const float p = (m[rr] == -INFINITY) ? 0.f : __expf(sc[nb][e] - m[rr]);
+                const float p = ex2_approx(sc[nb][e] - mu[rr]);
                 sc[nb][e] = p;
                 rs[rr] += p;
             }
