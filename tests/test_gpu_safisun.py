@@ -402,6 +402,22 @@ def test_tensor_core_attention_block_edges_with_dominant_keys(D, size, pos0, n):
     assert float(out[:, H * D:].float().abs().max()) == 0.0
     scale = ref.abs().amax(dim=(1, 2), keepdim=True).clamp(min=1.0)
     assert float(((got - ref).abs() / scale).max()) < 2e-2
+    # the same launch as an ordinary softmax: no sink, no cap (rows in a new block meet whole tiles that are masked for them)
+    rc = lib.atx_attn_local_prefill(qd.data_ptr(), kc.data_ptr(), vc.data_ptr(), bt.data_ptr(), nblk + 4, s0.data_ptr(),
+                                    sc.data_ptr(), sp.data_ptr(), 2, len(rows), None, 0, out.data_ptr(), H * D + 8,
+                                    H, G, D, D, bs, 0.3, 0.0, size, 0, 1.0, cabi.DT_BF16, 0, _st())
+    assert rc == 0, lib.atx_last_error()
+    torch.cuda.synchronize()
+    got = out[:, :H * D].float().cpu().double().view(len(rows), H, D)
+    pos = torch.arange(total)
+    seen = pos[:, None] >= pos[None, :]
+    if size:
+        seen = seen & ((pos[:, None] // size) == (pos[None, :] // size))
+    sco = torch.einsum("thd,jhd->htj", q, k.repeat_interleave(H // G, 1)) * 0.3
+    prob = torch.softmax(sco.masked_fill(~seen[None], float("-inf")), dim=-1)
+    ref = torch.einsum("htj,jhv->thv", prob, v.repeat_interleave(H // G, 1))[rows]
+    scale = ref.abs().amax(dim=(1, 2), keepdim=True).clamp(min=1.0)
+    assert float(((got - ref).abs() / scale).max()) < 2e-2
 
 
 @pytest.mark.parametrize("per_token", [False, True])
