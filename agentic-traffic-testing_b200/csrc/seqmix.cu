@@ -108,6 +108,16 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
     extern __shared__ __align__(16) float srow[];
     __shared__ float red[32];
     pdl_launch_dependents();
+    // One vector per thread covers the row (few rows, many threads): everything stays in registers, and the weights,
+    // which no kernel writes, are fetched before the wait for the producer of h and y.
+    const bool in_regs = VEC && W / 4 <= static_cast<int>(blockDim.x);
+    const bool on = in_regs && static_cast<int>(threadIdx.x) < W / 4 && static_cast<int>(blockIdx.x) < T;
+    float4 wp4 = make_float4(0.f, 0.f, 0.f, 0.f), vc4 = wp4, wq4 = wp4;
+    if (VEC && on) {
+        if (w_post) wp4 = ld4(w_post, threadIdx.x);
+        if (vec) vc4 = ld4(vec, threadIdx.x);
+        if (w_pre) wq4 = ld4(w_pre, threadIdx.x);
+    }
     pdl_wait();
     if (blockIdx.x >= T) {
         const long long nb = gridDim.x - T;
@@ -120,6 +130,27 @@ resid_norm_kernel(float* __restrict__ h, float* __restrict__ y, const XT* __rest
     const long long r = rows ? rows[t] : t;
     float* hr = h + r * W;
     float rs_y = 0.f;
+    if (VEC && in_regs) {
+        const int i = threadIdx.x;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f), a = v;
+        if (on) {
+            v = ld4(hr, i);
+            if (y) {
+                a = ld4(y + r * W, i);
+                if (zero_y) st4(y + r * W, i, make_float4(0.f, 0.f, 0.f, 0.f));
+            }
+        }
+        if (y) {
+            rs_y = rsqrtf(block_sum(a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w, red) / static_cast<float>(W) + eps);
+            v.x += a.x * rs_y * wp4.x, v.y += a.y * rs_y * wp4.y, v.z += a.z * rs_y * wp4.z, v.w += a.w * rs_y * wp4.w;
+        }
+        v.x += vc4.x, v.y += vc4.y, v.z += vc4.z, v.w += vc4.w;
+        if (on && (y || vec) && !rows) st4(hr, i, v);
+        if (!w_pre) return;
+        const float rs = rsqrtf(block_sum(v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w, red) / static_cast<float>(W) + eps);
+        if (on) st4(out + static_cast<long long>(t) * W, i, make_float4(v.x * rs * wq4.x, v.y * rs * wq4.y, v.z * rs * wq4.z, v.w * rs * wq4.w));
+        return;
+    }
     if (VEC) {   // W a multiple of 4 and every row 16-byte aligned (8 for bf16): four elements per load and store
         const int W4 = W / 4;
         float4* srow4 = reinterpret_cast<float4*>(srow);

@@ -647,7 +647,7 @@ def test_fma_gemm_and_norm_kernels_match_their_formulas():
         assert rc == 0, lib.atx_last_error()
         assert torch.allclose(out[:, :N].cpu().double(), x.cpu().double() @ w.cpu().double().T, atol=1e-4, rtol=tol)
         assert float(out[:, N:].abs().max()) == 0.0
-    for W in (70, 72):            # 70: element-wise path; 72: four elements per access
+    for W in (70, 72, 1028):      # element-wise; one four-element vector per thread, kept in registers; vectors in a loop
         h, y = torch.randn(T, W, generator=g, dtype=F64), 3.0 * torch.randn(T, W, generator=g, dtype=F64)
         wp, vec, wn = (torch.randn(W, generator=g, dtype=F64) for _ in range(3))
         hd, o = h.float().to(DEV), torch.zeros(T, W, device=DEV)
