@@ -275,6 +275,60 @@ def test_other_sizes():
         assert rel(got, want) < TOL[dtype], dtype
 
 
+_FF = {"ff": 72, "kind": "dense"}
+ODD_MODELS = {
+    "no_loop": lambda: model_cfg([mamba_layer(), parallel_layer(mlp=_FF), lightning_layer()], loop=None),
+    "loop_once_over_everything": lambda: model_cfg([mamba_layer(), parallel_layer(mlp=_FF), lightning_layer()],
+                                                   loop={"start": 0, "stop": 3, "times": 1}),
+    "loop_at_the_tail": lambda: model_cfg([lightning_layer(), mamba_layer(mlp=_FF), parallel_layer()],
+                                          loop={"start": 2, "stop": 3, "times": 3}),
+    "two_taps_four_groups": lambda: model_cfg([mamba_layer(heads=8, vdim=8, state=16, groups=4, norm_groups=4, conv=2),
+                                               lightning_layer()]),
+    "one_tap": lambda: model_cfg([mamba_layer(heads=2, vdim=8, state=16, groups=1, norm_groups=1, conv=1, mlp=_FF)]),
+    "eight_taps": lambda: model_cfg([mamba_layer(heads=2, vdim=8, state=32, groups=2, norm_groups=1, conv=8, mlp=_FF)]),
+    "every_head_its_own_kv_whole_head_rotated": lambda: model_cfg([parallel_layer(heads=4, kv=4, dim=16, vdim=16,
+                                                                                  rot_dims=16, size=7)]),
+    "blocks_of_one": lambda: model_cfg([parallel_layer(size=1), lightning_layer()]),
+    "block_larger_than_the_prompt": lambda: model_cfg([parallel_layer(size=4096, mlp=_FF)]),
+    "tensor_core_key_size_other_value_size": lambda: model_cfg([parallel_layer(heads=2, kv=1, dim=128, vdim=64, rot_dims=64,
+                                                                               size=40, mlp=_FF)], width=128),
+    "value_wider_than_key": lambda: model_cfg([parallel_layer(heads=4, kv=2, dim=64, vdim=128, rot_dims=32, size=100)],
+                                              width=128),
+    "heads_of_256": lambda: model_cfg([parallel_layer(heads=2, kv=1, dim=256, vdim=32, rot_dims=128, size=33),
+                                       lightning_layer(heads=2, dim=256, vdim=16, decay=[0.9, 0.99])], width=128),
+    "chunked_scan_96_keys_odd_values": lambda: model_cfg(
+        [lightning_layer(heads=2, dim=96, vdim=20, decay=[0.9, 0.999]),
+         mamba_layer(heads=6, vdim=12, state=128, groups=3, norm_groups=2, conv=4)], width=128),
+    "width_not_a_gemm_block": lambda: model_cfg([mamba_layer(), parallel_layer(mlp=_FF), lightning_layer()], width=72, vocab=77),
+    "one_head_one_rotated_pair": lambda: model_cfg([lightning_layer(heads=1, dim=32, vdim=32, decay=[0.97]),
+                                                    parallel_layer(heads=1, kv=1, dim=64, vdim=64, rot_dims=2, size=16)]),
+}
+
+
+@pytest.mark.parametrize("name", sorted(ODD_MODELS))
+def test_odd_configurations_whole_and_in_portions(name):
+    """Sizes on both sides of every kernel's fast path, each in fp32 and bf16: the whole prompt in one step, and cut into
+    70 | 2 | 1 | 1 | 64 | 3 | rest (a prompt-sized portion continues from single tokens and the other way round)."""
+    cfg = ODD_MODELS[name]()
+    wt = R.random_checkpoint(cfg, 3)
+    toks = tokens(150, vocab=cfg["vocab"], seed=9)
+    want = R.forward(cfg, wt, toks)
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(cfg, wt, dtype, max_model_len=160, max_num_batched_tokens=512)
+        a = whole(eng, "w", toks)
+        cuts = [70, 2, 1, 1, 64, 3]
+        cuts.append(len(toks) - sum(cuts))
+        parts, at = [], 0
+        for n in cuts:
+            parts.append(eng.feed([("p", toks[at:at + n], list(range(n)))], ["p"] if at + n == len(toks) else []))
+            at += n
+        b = np.concatenate(parts)
+        lim = 3e-5 if dtype == "float32" else 0.3      # bf16 operands through up to seven layer runs; fp32 is the sharp test
+        assert np.isfinite(a).all() and np.isfinite(b).all(), dtype
+        assert rel(a, want) < lim and rel(b, want) < lim, (dtype, rel(a, want), rel(b, want))
+        eng.runner.close()
+
+
 # ---- generation through the ordinary entry point ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("mode", ["plain", "chunked_prefill", "async", "graphs"])
