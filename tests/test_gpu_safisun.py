@@ -329,6 +329,101 @@ def test_odd_configurations_whole_and_in_portions(name):
         eng.runner.close()
 
 
+def drawn_model(rng):
+    """A model whose layer order, sizes, constants and looped block are drawn at random from sizes a real model could
+    have (key sizes on and off the tensor-core paths, widths on and off the GEMM's block, odd vocabularies)."""
+    def decays(h):
+        return [rng.choice([0.5, 0.61, 0.82, 0.92, 0.97, 0.988, 0.999, 0.9999]) for _ in range(h)]
+
+    def lightning():
+        h = rng.choice([1, 2, 3, 4, 6, 8])
+        return {"decay": decays(h), "dim": rng.choice([16, 32, 48, 64, 96, 128]), "heads": h,
+                "vdim": rng.choice([16, 24, 32, 48, 64, 128])}
+
+    def mamba():
+        g = rng.choice([1, 2, 4])
+        h = g * rng.choice([1, 2, 3])
+        return {"conv": rng.choice([2, 3, 4, 5]), "groups": g, "heads": h,
+                "norm_groups": rng.choice([x for x in (1, 2, 3, 4, 6) if h % x == 0]),
+                "state": rng.choice([16, 32, 64, 128]), "vdim": rng.choice([16, 32, 48, 64])}
+
+    def softmax_side():
+        kv = rng.choice([1, 2, 4])
+        d = rng.choice([32, 64, 96, 128])
+        return {"dim": d, "heads": kv * rng.choice([1, 2, 3, 4]), "kv_heads": kv,
+                "mask": {"size": rng.choice([16, 32, 48, 64, 100, 128])},
+                "rot": {"base": rng.choice([1e4, 5e5, 1e6]), "dims": rng.choice([x for x in (2, 16, 32, 64, 128) if x <= d])},
+                "scale": rng.choice([d ** -0.5, 0.05, 0.2]), "softcap": rng.choice([20.0, 30.0, 50.0]),
+                "vdim": rng.choice([32, 64, 128, d])}
+
+    def layer(kind):
+        mixer = {"lightning": lightning, "mamba2": mamba,
+                 "parallel": lambda: {"left": softmax_side(), "left_scale": rng.choice([0.5, 0.8, 1.0]),
+                                      "right": lightning(), "right_scale": rng.choice([1.0, 1.1, 0.6])}}[kind]()
+        return {"type": kind, "mixer": mixer, "mlp": rng.choice([None, {"ff": rng.choice([128, 192, 320, 500]), "kind": "dense"}])}
+
+    n = rng.randint(3, 6)
+    kinds = ["lightning", "mamba2", "parallel"] + [rng.choice(["lightning", "mamba2", "parallel"]) for _ in range(n - 3)]
+    rng.shuffle(kinds)
+    a = rng.randint(0, n - 1)
+    loop = rng.choice([None, {"start": a, "stop": rng.randint(a + 1, n), "times": rng.choice([1, 2, 3])}])
+    cfg = model_cfg([layer(k) for k in kinds], width=rng.choice([64, 128, 160, 192, 256, 320]),
+                    vocab=rng.choice([256, 320, 500, 1000, 1027]), loop=loop)
+    cfg["norm"]["eps"] = rng.choice([1e-5, 1e-6])
+    return cfg
+
+
+@pytest.mark.parametrize("draw", range(8))
+def test_drawn_models_whole_cut_and_mixed(draw):
+    """Three unequal requests of a drawn model: each whole, the longest in portions with its last tokens one by one, then
+    all three in steps where a request may bring a portion, one token or nothing. fp32 is held to rounding on every row;
+    bf16 to its typical row (single rows of a random model are ill-conditioned by factors of ten to twenty in both types)."""
+    import random
+    rng = random.Random(4000 + draw)
+    cfg = drawn_model(rng)
+    wt = R.random_checkpoint(cfg, 70 + draw)
+    V = cfg["vocab"]
+    reqs = {"a": tokens(rng.randint(150, 330), V, draw), "b": tokens(rng.randint(70, 200), V, draw + 100),
+            "c": tokens(rng.randint(2, 90), V, draw + 200)}
+    want = {k: R.forward(cfg, wt, v) for k, v in reqs.items()}
+    for dtype in ("float32", "bfloat16"):
+        eng = engine(cfg, wt, dtype, max_model_len=384, max_num_batched_tokens=1024, max_logit_rows=1024, num_gpu_blocks=48)
+        rows = [rel_rows(eng.feed([(k, v, list(range(len(v))))], [k]), want[k]) for k, v in reqs.items()]
+        v, at, parts = reqs["a"], 0, []
+        while at < len(v):
+            n = 1 if len(v) - at <= 40 else min(rng.choice([2, 3, 7, 64, 65, 100, 130]), len(v) - at - 40)
+            parts.append(eng.feed([("a", v[at:at + n], list(range(n)))], ["a"] if at + n == len(v) else []))
+            at += n
+        rows.append(rel_rows(np.concatenate(parts), want["a"]))
+        pos, got, live = {k: 0 for k in reqs}, {k: [] for k in reqs}, ["a", "b", "c"]
+        while live:
+            entries, end, taken = [], [], []
+            for k in list(live):
+                if len(live) > 1 and rng.random() < 0.25:
+                    continue                                   # left out of this step, goes on later
+                n = min(len(reqs[k]) - pos[k], rng.choice([1, 1, 1, 2, 5, 31, 64, 90]))
+                entries.append((k, reqs[k][pos[k]:pos[k] + n], list(range(n))))
+                taken.append((k, n))
+                pos[k] += n
+                if pos[k] == len(reqs[k]):
+                    end.append(k)
+                    live.remove(k)
+            if entries:
+                out, o = eng.feed(entries, end), 0
+                for k, n in taken:
+                    got[k].append(out[o:o + n])
+                    o += n
+        rows += [rel_rows(np.concatenate(got[k]), want[k]) for k in reqs]
+        assert eng.allocator.num_free == eng.allocator.num_blocks and eng.state_slots.num_free == 4
+        r = torch.cat(rows)
+        assert torch.isfinite(r).all(), dtype
+        if dtype == "float32":
+            assert float(r.max()) < 1e-4 and float(r.median()) < 5e-6, (float(r.max()), float(r.median()))
+        else:
+            assert float(r.max()) < 0.6 and float(r.median()) < 0.03, (float(r.max()), float(r.median()))
+        eng.runner.close()
+
+
 # ---- generation through the ordinary entry point ---------------------------------------------------------------------------
 
 @pytest.mark.parametrize("mode", ["plain", "chunked_prefill", "async", "graphs"])
