@@ -23,6 +23,13 @@ __device__ __forceinline__ float ldx<__nv_bfloat16>(const __nv_bfloat16* p, long
 }
 __device__ __forceinline__ void stx(float* p, long long i, float v) { p[i] = v; }
 __device__ __forceinline__ void stx(__nv_bfloat16* p, long long i, float v) { p[i] = __float2bfloat16_rn(v); }
+// Two adjacent elements in one access; i is even and p + i is aligned to the pair.
+__device__ __forceinline__ void stx2(float* p, long long i, float a, float b) {
+    *reinterpret_cast<float2*>(p + i) = make_float2(a, b);
+}
+__device__ __forceinline__ void stx2(__nv_bfloat16* p, long long i, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p + i) = __floats2bfloat162_rn(a, b);
+}
 
 // ---- bias, whole-projection RMS norm, partial rotation, page scatter ----------------------------------------------
 // One block per row. rot: [max_pos, rot_dims] fp32, cos of the rot_dims/2 angles then their sines.
@@ -45,17 +52,45 @@ qk_prepare_kernel(const float* __restrict__ proj, long long ld, int q_off, int k
     float* sk = sm + nq;
     const float* row = proj + t * ld;
     float ssq = 0.f, ssk = 0.f;
-    for (int i = threadIdx.x; i < nq; i += blockDim.x) {
-        float v = row[q_off + i];
-        if (bq) v += ldx(bq, i);
-        sq[i] = v;
-        ssq += v * v;
-    }
-    for (int i = threadIdx.x; i < nk; i += blockDim.x) {
-        float v = row[k_off + i];
-        if (bk) v += ldx(bk, i);
-        sk[i] = v;
-        ssk += v * v;
+    // pairs in one access when the row, both offsets and the outputs keep a pair aligned (the usual case)
+    const bool pairs = ((q_off | k_off | nq | D) & 1) == 0 && (ld & 1) == 0 &&
+                       (reinterpret_cast<unsigned long long>(proj) & 7) == 0 &&
+                       (reinterpret_cast<unsigned long long>(q_out) & 7) == 0 &&
+                       (reinterpret_cast<unsigned long long>(k_cache) & 7) == 0;
+    if (pairs) {
+        #pragma unroll 4
+        for (int i = 2 * threadIdx.x; i < nq; i += 2 * blockDim.x) {
+            float2 v = *reinterpret_cast<const float2*>(row + q_off + i);
+            if (bq) {
+                v.x += ldx(bq, i);
+                v.y += ldx(bq, i + 1);
+            }
+            *reinterpret_cast<float2*>(sq + i) = v;
+            ssq += v.x * v.x + v.y * v.y;
+        }
+        #pragma unroll 4
+        for (int i = 2 * threadIdx.x; i < nk; i += 2 * blockDim.x) {
+            float2 v = *reinterpret_cast<const float2*>(row + k_off + i);
+            if (bk) {
+                v.x += ldx(bk, i);
+                v.y += ldx(bk, i + 1);
+            }
+            *reinterpret_cast<float2*>(sk + i) = v;
+            ssk += v.x * v.x + v.y * v.y;
+        }
+    } else {
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) {
+            float v = row[q_off + i];
+            if (bq) v += ldx(bq, i);
+            sq[i] = v;
+            ssq += v * v;
+        }
+        for (int i = threadIdx.x; i < nk; i += blockDim.x) {
+            float v = row[k_off + i];
+            if (bk) v += ldx(bk, i);
+            sk[i] = v;
+            ssk += v * v;
+        }
     }
     ssq = warp_sum(ssq);
     ssk = warp_sum(ssk);
@@ -76,6 +111,7 @@ qk_prepare_kernel(const float* __restrict__ proj, long long ld, int q_off, int k
     const int half = rot_dims / 2;
     const int blk = slot / bs, off = slot - blk * bs;
     // q and k: work items are pairs of adjacent dimensions
+    #pragma unroll 4
     for (int e = threadIdx.x; e < (nq + nk) / 2; e += blockDim.x) {
         const bool isq = e < nq / 2;
         const int p = isq ? e : e - nq / 2;  // pair index inside q or k
@@ -104,12 +140,20 @@ qk_prepare_kernel(const float* __restrict__ proj, long long ld, int q_off, int k
             b = rb;
         }
         if (isq) {
-            stx(q_out, t * nq + i0, a);
-            stx(q_out, t * nq + i0 + 1, b);
+            if (pairs) {
+                stx2(q_out, t * nq + i0, a, b);
+            } else {
+                stx(q_out, t * nq + i0, a);
+                stx(q_out, t * nq + i0 + 1, b);
+            }
         } else {
             const long long base = ((static_cast<long long>(blk) * G + head) * bs + off) * D + d;
-            stx(k_cache, base, a);
-            stx(k_cache, base + 1, b);
+            if (pairs) {
+                stx2(k_cache, base, a, b);
+            } else {
+                stx(k_cache, base, a);
+                stx(k_cache, base + 1, b);
+            }
         }
     }
     for (int i = threadIdx.x; i < G * Vd; i += blockDim.x) {

@@ -73,8 +73,14 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const int* __restrict__
     const int t = blockIdx.x;
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
-    for (int i = threadIdx.x; i < W; i += blockDim.x)
-        out[static_cast<long long>(t) * W + i] = ldf(table, static_cast<long long>(id) * W + i);
+    const XT* src = table + static_cast<long long>(id) * W;
+    float* dst = out + static_cast<long long>(t) * W;
+    if ((W & 3) == 0 && ((reinterpret_cast<unsigned long long>(table) | reinterpret_cast<unsigned long long>(out)) & 15) == 0) {
+#pragma unroll 4
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) st4(dst, i, ld4(src, i));  // four elements per access
+        return;
+    }
+    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = ldf(src, i);
 }
 
 // ---- [x ; x0]: the input of the projection that re-enters a block of layers ---------------------------------------
@@ -88,6 +94,17 @@ __global__ void __launch_bounds__(128) concat_embed_kernel(const float* __restri
     int id = ids[t];
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
     XT* o = out + static_cast<long long>(t) * 2 * W;
+    if ((W & 3) == 0 && ((reinterpret_cast<unsigned long long>(table) | reinterpret_cast<unsigned long long>(out) |
+                          reinterpret_cast<unsigned long long>(h)) & 15) == 0) {
+        const float* hr = h + static_cast<long long>(t) * W;
+        const XT* src = table + static_cast<long long>(id) * W;
+#pragma unroll 4
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {  // four elements per access
+            st4(o, i, ld4(hr, i));
+            st4(o + W, i, ld4(src, i));
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < W; i += blockDim.x) {
         stf(o, i, h[static_cast<long long>(t) * W + i]);
         o[W + i] = table[static_cast<long long>(id) * W + i];
