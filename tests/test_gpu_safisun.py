@@ -818,3 +818,18 @@ def test_fma_gemm_and_norm_kernels_match_their_formulas():
                                     1 if mode == 0 else groups, 1e-5, mode, 0.7, cabi.DT_F32, 0, _st())
             assert rc == 0, lib.atx_last_error()
             assert torch.allclose(o.cpu().double(), want, atol=1e-5), mode
+    for W in (70, 72):      # embedding rows: element-wise; four elements per access
+        for xt, dt in ((torch.float32, cabi.DT_F32), (torch.bfloat16, cabi.DT_BF16)):
+            V = 9
+            table = torch.randn(V, W, generator=g).to(xt).to(DEV)
+            ids = torch.tensor([3, 0, 8, 8, 5], dtype=torch.int32, device=DEV)
+            n = ids.numel()
+            out = torch.zeros(n, W, device=DEV)
+            rc = lib.atx_embed_rows(ids.data_ptr(), table.data_ptr(), out.data_ptr(), n, W, V, dt, 0, _st())
+            assert rc == 0, lib.atx_last_error()
+            assert torch.equal(out, table[ids.long()].float())
+            hh = torch.randn(n, W, generator=g).to(DEV)
+            both = torch.zeros(n, 2 * W, dtype=xt, device=DEV)
+            rc = lib.atx_concat_embed(hh.data_ptr(), ids.data_ptr(), table.data_ptr(), both.data_ptr(), n, W, V, dt, 0, _st())
+            assert rc == 0, lib.atx_last_error()
+            assert torch.equal(both[:, :W], hh.to(xt)) and torch.equal(both[:, W:], table[ids.long()])
