@@ -37,7 +37,29 @@ EXPORTS = [
     "atx_conv_dt", "atx_conv_state_update", "atx_linear_recurrence", "atx_qk_prepare", "atx_attn_local",
     "atx_attn_local_prefill", "atx_attn_local_prefill_supported",
     "atx_linear_recurrence_chunked", "atx_linear_recurrence_chunked_supported",
+    "atx_embed_rows_scaled", "atx_tanh_norm", "atx_unary_act", "atx_head_prepare", "atx_head_gemm", "atx_attn_window",
 ]
+ACT_RELU2 = 0
+ACT_GELU_TANH = 1
+HEAD_DST_ROWS = 0
+HEAD_DST_PAGES = 1
+HEAD_SEGS_MAX = 4
+
+
+class HeadSeg(C.Structure):
+    """atx_head_seg: one slice of a fused projection row for atx_head_prepare (include/atx_b200.h)."""
+
+    _fields_ = [("src_off", C.c_int), ("src_stride", C.c_int), ("heads", C.c_int), ("width", C.c_int),
+                ("norm_dims", C.c_int), ("rot_off", C.c_int), ("rot_dims", C.c_int),
+                ("dst_kind", C.c_int), ("dst_off", C.c_int), ("dst_stride", C.c_int),
+                ("mix", C.c_float), ("reserved", C.c_int),
+                ("norm_w", C.c_void_p), ("rot", C.c_void_p), ("mix_src", C.c_void_p), ("save", C.c_void_p),
+                ("dst", C.c_void_p), ("dst_ld", C.c_longlong)]
+
+
+def head_segs(*segs: "HeadSeg"):
+    """A C array of segments for atx_head_prepare."""
+    return (HeadSeg * len(segs))(*segs)
 
 
 class AtxError(RuntimeError):
@@ -117,6 +139,13 @@ def load() -> C.CDLL:
     lib.atx_attn_local_prefill_supported.argtypes = [i32, i32, i32]
     lib.atx_attn_local_prefill.argtypes = [vp, vp, vp, vp, i32, vp, vp, vp, i32, i32, vp, i64, vp, i64, i32, i32, i32, i32,
                                            i32, f32, f32, i32, i32, f32, i32, i32, vp]
+    lib.atx_embed_rows_scaled.argtypes = [vp, vp, vp, i32, i32, i32, f32, i32, i32, vp]
+    lib.atx_tanh_norm.argtypes = [vp, vp, f32, vp, vp, vp, i32, i32, vp, i64, i32, i32, vp]
+    lib.atx_unary_act.argtypes = [vp, i64, vp, i64, i32, i32, i32, i32, i32, vp]
+    lib.atx_head_prepare.argtypes = [vp, i64, C.POINTER(HeadSeg), i32, vp, vp, i32, i32, f32, i32, i32, vp]
+    lib.atx_head_gemm.argtypes = [vp, i32, i64, i32, i32, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp]
+    lib.atx_attn_window.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32,
+                                    f32, f32, i32, i32, vp, vp, i32, f32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

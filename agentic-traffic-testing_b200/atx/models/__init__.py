@@ -10,9 +10,9 @@ from typing import Optional
 
 
 def _entries():
-    from . import safisun
+    from . import gopopel, safisun
 
-    return {"safisun": safisun}
+    return {"safisun": safisun, "gopopel": gopopel}
 
 
 def _module(arch: str):

@@ -33,6 +33,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from .. import _cabi
+from .common import _Linear, _use_tc, rotation_table  # noqa: F401  (shared by every layer-list family)
 
 # ---- configuration --------------------------------------------------------------------------------------------------
 
@@ -221,10 +222,6 @@ class _Layer:
         self.gu_interleaved = False
 
 
-def _use_tc(dtype: torch.dtype, k: int) -> bool:
-    return dtype == torch.bfloat16 and k % 64 == 0
-
-
 class Weights:
     def __init__(self, cfg: Config, device: torch.device, dtype: torch.dtype):
         self.cfg, self.device, self.dtype = cfg, device, dtype
@@ -347,45 +344,6 @@ class Weights:
 
 
 # ---- the layer program ------------------------------------------------------------------------------------------------
-
-
-class _Linear:
-    """out[t, :] = X[t, :] @ W^T (fp32 out): the tcgen05 GEMM when the operands are bf16 and K is a multiple of its
-    64-element block, else the FMA-pipe GEMM (fp32 operands, odd reduction sizes)."""
-
-    def __init__(self, lib, w: torch.Tensor, x_buf: torch.Tensor, dt: int):
-        self.lib, self.w, self.x, self.dt = lib, w, x_buf, dt
-        self.N, self.K = int(w.shape[0]), int(w.shape[1])
-        assert x_buf.shape[1] == self.K and x_buf.is_contiguous() and w.is_contiguous()
-        self.plan = _cabi.GemmPlan(w, x_buf) if _use_tc(w.dtype, self.K) else None
-
-    def accumulates(self, T: int) -> bool:
-        """Decode-sized steps stream the weights once: the tcgen05 GEMM then cuts K over enough CTAs to fill the GPU
-        and ADDS its partial sums, so the target has to be zero before the launch."""
-        return self.plan is not None and T <= 64
-
-    def run(self, out_ptr: int, ldo: int, T: int, flags: int, st: int, mode: int = _cabi.GEMM_STORE_F32,
-            zeroed: bool = False) -> None:
-        if self.plan is not None:
-            if zeroed and mode == _cabi.GEMM_STORE_F32 and self.accumulates(T):
-                rc = self.lib.atx_gemm_run(self.plan._h, out_ptr, ldo, T, _cabi.GEMM_ADD_F32, 0, flags, st)
-            else:
-                rc = self.lib.atx_gemm_run(self.plan._h, out_ptr, ldo, T, mode, 1 if mode == _cabi.GEMM_STORE_F32 else 0,
-                                           flags, st)
-        else:
-            assert mode == _cabi.GEMM_STORE_F32
-            rc = self.lib.atx_gemm_simple(self.w.data_ptr(), self.K, self.x.data_ptr(), self.K, out_ptr, ldo, T, self.N,
-                                          self.K, 0, self.dt, flags, st)
-        if rc != 0:
-            raise _cabi.AtxError(f"atx error {rc}: {self.lib.atx_last_error().decode()}")
-
-
-def rotation_table(base: float, dims: int, max_pos: int, device: torch.device) -> torch.Tensor:
-    """[max_pos, dims] fp32: cos then sin of p * base^(-2i/dims), i < dims/2, evaluated in float64 on the host."""
-    i = torch.arange(dims // 2, dtype=torch.float64)
-    ang = torch.arange(max_pos, dtype=torch.float64)[:, None] * torch.pow(torch.tensor(base, dtype=torch.float64),
-                                                                          -2.0 * i / dims)[None, :]
-    return torch.cat((ang.cos(), ang.sin()), -1).to(torch.float32).contiguous().to(device)
 
 
 class Program:

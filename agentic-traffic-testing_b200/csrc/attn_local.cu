@@ -165,15 +165,16 @@ qk_prepare_kernel(const float* __restrict__ proj, long long ld, int q_off, int k
 }
 
 // ---- attention ---------------------------------------------------------------------------------------------------
-constexpr int kMaxVdPerLane = 8;  // Vd <= 256
+constexpr int kMaxVdPerLane = 16;  // Vd <= 512; the kernel is instantiated for 2, 4, 8 and 16 value elements per lane
 
-template <typename XT>
+template <typename XT, int NV>
 __global__ void __launch_bounds__(128)
 attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, const XT* __restrict__ v_cache,
                   const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ tok_seq,
                   const int* __restrict__ positions, const float* __restrict__ gate, long long ldg,
                   XT* __restrict__ out, long long ldo, int H, int G, int D, int Vd, int bs, float scale, float softcap,
-                  int chunk, int sink, float out_scale) {
+                  int chunk, int sink, float out_scale, long long k_row, long long v_row, int window,
+                  const float* __restrict__ slopes, const float* __restrict__ sinks) {
     extern __shared__ float sm[];
     pdl_launch_dependents();
     pdl_wait();
@@ -184,16 +185,20 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
     if (s < 0 || h >= H) return;
     const int g = h / (H / G);
     const int pos = positions[t];
-    const int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    int lo = chunk > 0 ? (pos / chunk) * chunk : 0;
+    if (window > 0) lo = max(lo, pos - window + 1);   // sliding window: the row itself and the window - 1 tokens before it
+    const float slope = slopes ? slopes[h] : 0.f;
     float* sq = sm + warp * D;
     for (int d = lane; d < D; d += 32) sq[d] = ldx(q, (t * H + h) * D + d) * scale;
     __syncwarp();
     const int* bt = block_tables + static_cast<long long>(s) * max_blocks;
-    // the sink is a key with score 0 and no value: the running maximum starts at 0 and the denominator at 1
-    float m = sink ? 0.f : -INFINITY, l = sink ? 1.f : 0.f;
-    float acc[kMaxVdPerLane];
+    // the sink is a key with a fixed score (0, or a learned number per head) and no value: the running maximum starts
+    // at that score and the denominator at 1
+    const bool has_sink = sink || sinks;
+    float m = has_sink ? (sinks ? sinks[h] : 0.f) : -INFINITY, l = has_sink ? 1.f : 0.f;
+    float acc[NV];
 #pragma unroll
-    for (int i = 0; i < kMaxVdPerLane; ++i) acc[i] = 0.f;
+    for (int i = 0; i < NV; ++i) acc[i] = 0.f;
     for (int k0 = lo; k0 <= pos; k0 += 32) {
         const int kp = k0 + lane;
         float sc = -INFINITY;
@@ -201,25 +206,26 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
         if (kp <= pos) {
             const int blk = bt[kp / bs];
             const long long tokslot = (static_cast<long long>(blk) * G + g) * bs + (kp % bs);
-            const XT* kr = k_cache + tokslot * D;
-            vbase = tokslot * Vd;
+            const XT* kr = k_cache + tokslot * k_row;
+            vbase = tokslot * v_row;
             float dot = 0.f;
             for (int d = 0; d < D; ++d) dot = fmaf(sq[d], ldx(kr, d), dot);
             sc = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
+            sc -= slope * static_cast<float>(pos - kp);   // penalty per unit of distance
         }
         const float mt = fmaxf(m, warp_max(sc));
         const float corr = (m == -INFINITY) ? 0.f : expf(m - mt);
         const float p = (kp <= pos) ? expf(sc - mt) : 0.f;
         l = l * corr + warp_sum(p);
 #pragma unroll
-        for (int i = 0; i < kMaxVdPerLane; ++i) acc[i] *= corr;
+        for (int i = 0; i < NV; ++i) acc[i] *= corr;
         m = mt;
         const int nk = min(32, pos - k0 + 1);
         for (int j = 0; j < nk; ++j) {
             const float pj = __shfl_sync(0xffffffffu, p, j);
             const long long vb = __shfl_sync(0xffffffffu, vbase, j);
 #pragma unroll
-            for (int i = 0; i < kMaxVdPerLane; ++i) {
+            for (int i = 0; i < NV; ++i) {
                 const int d = lane + 32 * i;
                 if (d < Vd) acc[i] = fmaf(pj, ldx(v_cache, vb + d), acc[i]);
             }
@@ -228,7 +234,7 @@ attn_local_kernel(const XT* __restrict__ q, const XT* __restrict__ k_cache, cons
     float gmul = out_scale / l;
     if (gate) gmul *= 1.f / (1.f + expf(-gate[t * ldg + h]));
 #pragma unroll
-    for (int i = 0; i < kMaxVdPerLane; ++i) {
+    for (int i = 0; i < NV; ++i) {
         const int d = lane + 32 * i;
         if (d < Vd) stx(out, t * ldo + static_cast<long long>(h) * Vd + d, acc[i] * gmul);
     }
@@ -573,10 +579,21 @@ int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, cons
                    const int* tok_seq, const int* positions, const float* gate, long long ldg, void* out, long long ldo,
                    int T, int H, int G, int D, int Vd, int block_size, float scale, float softcap, int chunk, int sink,
                    float out_scale, int dtype, int flags, atx_stream_t stream) {
-    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_local: null pointer");
+    return atx_attn_window(q, k_cache, v_cache, D, Vd, block_tables, max_blocks, tok_seq, positions, gate, ldg, out, ldo, T,
+                           H, G, D, Vd, block_size, scale, softcap, chunk, 0, nullptr, nullptr, sink, out_scale, dtype,
+                           flags, stream);
+}
+
+int atx_attn_window(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                    const int* block_tables, int max_blocks, const int* tok_seq, const int* positions, const float* gate,
+                    long long ldg, void* out, long long ldo, int T, int H, int G, int D, int Vd, int block_size,
+                    float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks, int sink,
+                    float out_scale, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_window: null pointer");
     ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && Vd > 0 && Vd <= 32 * kMaxVdPerLane && block_size > 0 &&
-                    chunk >= 0,
-                "atx_attn_local: bad shape T=%d H=%d G=%d D=%d Vd=%d (Vd <= %d)", T, H, G, D, Vd, 32 * kMaxVdPerLane);
+                    chunk >= 0 && window >= 0 && k_row >= D && v_row >= Vd,
+                "atx_attn_window: bad shape T=%d H=%d G=%d D=%d Vd=%d (Vd <= %d) k_row=%lld v_row=%lld", T, H, G, D, Vd,
+                32 * kMaxVdPerLane, k_row, v_row);
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
     cfg.gridDim = dim3(T, (H + 3) / 4);
@@ -589,19 +606,26 @@ int atx_attn_local(const void* q, const void* k_cache, const void* v_cache, cons
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
+#define ATX_ATTN_ROW_LAUNCH(XT_, NV_)                                                                                  \
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_kernel<XT_, NV_>, reinterpret_cast<const XT_*>(q),                    \
+                                reinterpret_cast<const XT_*>(k_cache), reinterpret_cast<const XT_*>(v_cache),          \
+                                block_tables, max_blocks, tok_seq, positions, gate, ldg, reinterpret_cast<XT_*>(out),  \
+                                ldo, H, G, D, Vd, block_size, scale, softcap, chunk, sink, out_scale, k_row, v_row,    \
+                                window, slopes, sinks))
+#define ATX_ATTN_ROW_BY_VD(XT_)                        \
+    do {                                               \
+        if (Vd <= 64) ATX_ATTN_ROW_LAUNCH(XT_, 2);     \
+        else if (Vd <= 128) ATX_ATTN_ROW_LAUNCH(XT_, 4); \
+        else if (Vd <= 256) ATX_ATTN_ROW_LAUNCH(XT_, 8); \
+        else ATX_ATTN_ROW_LAUNCH(XT_, 16);             \
+    } while (0)
     if (dtype == ATX_DT_F32) {
-        ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_kernel<float>, reinterpret_cast<const float*>(q),
-                                    reinterpret_cast<const float*>(k_cache), reinterpret_cast<const float*>(v_cache),
-                                    block_tables, max_blocks, tok_seq, positions, gate, ldg,
-                                    reinterpret_cast<float*>(out), ldo, H, G, D, Vd, block_size, scale, softcap, chunk,
-                                    sink, out_scale));
+        ATX_ATTN_ROW_BY_VD(float);
     } else {
-        using B = __nv_bfloat16;
-        ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_kernel<B>, reinterpret_cast<const B*>(q),
-                                    reinterpret_cast<const B*>(k_cache), reinterpret_cast<const B*>(v_cache), block_tables,
-                                    max_blocks, tok_seq, positions, gate, ldg, reinterpret_cast<B*>(out), ldo, H, G, D,
-                                    Vd, block_size, scale, softcap, chunk, sink, out_scale));
+        ATX_ATTN_ROW_BY_VD(__nv_bfloat16);
     }
+#undef ATX_ATTN_ROW_BY_VD
+#undef ATX_ATTN_ROW_LAUNCH
     return ATX_OK;
 }
 

@@ -67,7 +67,7 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 // ---- embedding rows -------------------------------------------------------------------------------------------
 template <typename XT>
 __global__ void __launch_bounds__(128) embed_rows_kernel(const int* __restrict__ ids, const XT* __restrict__ table,
-                                                         float* __restrict__ out, int W, int V) {
+                                                         float* __restrict__ out, int W, int V, float scale) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
@@ -77,10 +77,14 @@ __global__ void __launch_bounds__(128) embed_rows_kernel(const int* __restrict__
     float* dst = out + static_cast<long long>(t) * W;
     if ((W & 3) == 0 && ((reinterpret_cast<unsigned long long>(table) | reinterpret_cast<unsigned long long>(out)) & 15) == 0) {
 #pragma unroll 4
-        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) st4(dst, i, ld4(src, i));  // four elements per access
+        for (int i = threadIdx.x; i < W / 4; i += blockDim.x) {  // four elements per access
+            float4 v = ld4(src, i);
+            v.x *= scale, v.y *= scale, v.z *= scale, v.w *= scale;   // scale 1 leaves the row as it is stored
+            st4(dst, i, v);
+        }
         return;
     }
-    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = ldf(src, i);
+    for (int i = threadIdx.x; i < W; i += blockDim.x) dst[i] = ldf(src, i) * scale;
 }
 
 // ---- [x ; x0]: the input of the projection that re-enters a block of layers ---------------------------------------
@@ -631,6 +635,11 @@ extern "C" {
 
 int atx_embed_rows(const int* ids, const void* table, float* out, int T, int W, int V, int dtype, int flags,
                    atx_stream_t stream) {
+    return atx_embed_rows_scaled(ids, table, out, T, W, V, 1.f, dtype, flags, stream);
+}
+
+int atx_embed_rows_scaled(const int* ids, const void* table, float* out, int T, int W, int V, float scale, int dtype,
+                          int flags, atx_stream_t stream) {
     ATX_REQUIRE(ids && table && out, "atx_embed_rows: null pointer");
     ATX_REQUIRE(T > 0 && W > 0 && V > 0, "atx_embed_rows: bad shape T=%d W=%d V=%d", T, W, V);
     cudaLaunchConfig_t cfg = {};
@@ -640,7 +649,7 @@ int atx_embed_rows(const int* ids, const void* table, float* out, int T, int W, 
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl2(cfg, attr, flags);
     ATX_DISPATCH_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, embed_rows_kernel<XT>, ids,
-                                                       reinterpret_cast<const XT*>(table), out, W, V)));
+                                                       reinterpret_cast<const XT*>(table), out, W, V, scale)));
     return ATX_OK;
 }
 

@@ -300,6 +300,67 @@ int atx_attn_local_prefill(const void* q, const void* k_cache, const void* v_cac
                            int Vd, int block_size, float scale, float softcap, int chunk, int sink, float out_scale,
                            int dtype, int flags, atx_stream_t stream);
 
+/* ---- Attention variants and per-head operations that further designs are built from ---------------------------------
+ * (Gopopel: sliding-window attention with a distance penalty and a learned sink, latent attention in its absorbed
+ * form, tanh norm, squared-ReLU feed-forward. Every constant is an argument.) */
+
+/* out[t, :] = table[ids[t], :] * scale as fp32. */
+int atx_embed_rows_scaled(const int* ids, const void* table, float* out, int T, int W, int V, float scale, int dtype,
+                          int flags, atx_stream_t stream);
+/* out[t, :] = tanh(alpha * x[r, :]) * w + b, r = rows ? rows[t] : t: a norm without row statistics. x fp32 [., W], w / b /
+ * out of the element type. Spare CTAs clear zero_ptr / zero_bytes (a multiple of 16): the accumulator of a split-K GEMM
+ * that runs next. */
+int atx_tanh_norm(const float* x, const int* rows, float alpha, const void* w, const void* b, void* out, int T, int W,
+                  void* zero_ptr, long long zero_bytes, int dtype, int flags, atx_stream_t stream);
+#define ATX_ACT_RELU2 0     /* max(z, 0)^2 */
+#define ATX_ACT_GELU_TANH 1 /* z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) */
+/* out[t, i] = act(in[t, i]) (fp32 in, element type out). */
+int atx_unary_act(const float* in, long long ldi, void* out, long long ldo, int T, int I, int kind, int dtype, int flags,
+                  atx_stream_t stream);
+
+/* One slice of a fused projection row, cut into `heads` heads of `width` elements (head h starts at column
+ * src_off + h * src_stride). Per head, in this order: the first norm_dims elements are divided by their root mean square
+ * (eps under the root) and multiplied by norm_w; the elements [rot_off, rot_off + rot_dims) are rotated in adjacent pairs
+ * by the angles of rot [max_pos, rot_dims] (cosines, then sines) at the row's position; `save` (fp32 [T, heads * width])
+ * receives the result; with mix_src (same shape) the result becomes (1 - mix) * result + mix * mix_src. It is written as
+ * the element type to rows (dst [T, dst_ld], head h at column dst_off + h * dst_stride) or to pages
+ * (dst [blocks, heads, block_size, dst_stride], at the row's slot, from column dst_off of the token's row). */
+#define ATX_HEAD_DST_ROWS 0
+#define ATX_HEAD_DST_PAGES 1
+#define ATX_HEAD_SEGS_MAX 4
+typedef struct atx_head_seg {
+    int src_off, src_stride, heads, width;
+    int norm_dims, rot_off, rot_dims;
+    int dst_kind, dst_off, dst_stride;
+    float mix;
+    int reserved;
+    const void* norm_w;
+    const float* rot;
+    const float* mix_src;
+    float* save;
+    void* dst;
+    long long dst_ld;
+} atx_head_seg;
+int atx_head_prepare(const float* src, long long ld, const atx_head_seg* segs, int n_segs, const int* positions,
+                     const int* slots, int T, int block_size, float eps, int dtype, int flags, atx_stream_t stream);
+/* A small matrix product per head: out[t, o_off + h * o_head_stride + n] = sum_k X[t, x_off + h * x_head_stride + k] *
+ * W[(h * N + n) * ldw + k], times sigmoid(gate[t, h * N + n]) if gate. X fp32 (x_f32 != 0) or of the element type, gate
+ * fp32, W and out of the element type. */
+int atx_head_gemm(const void* X, int x_f32, long long ldx, int x_off, int x_head_stride, const void* W, long long ldw,
+                  const float* gate, long long ldg, void* out, long long ldo, int o_off, int o_head_stride, int T,
+                  int heads, int N, int K, int dtype, int flags, atx_stream_t stream);
+
+/* atx_attn_local with the remaining options of the kernel: a token's key row holds k_row elements (the first D are the
+ * key) and its value row v_row (the first Vd are the value), so that keys and values may live in one page array (latent
+ * attention: v_cache = k_cache, Vd leading elements); window > 0: a query at p sees only keys j > p - window (on top of
+ * j <= p and of `chunk`); slopes [H] (nullable): slopes[h] * (p - j) is taken off the score after scale and cap;
+ * sinks [H] (nullable): exp(sinks[h]) is added to the softmax denominator (sink != 0 without sinks: exp(0)). */
+int atx_attn_window(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                    const int* block_tables, int max_blocks, const int* tok_seq, const int* positions, const float* gate,
+                    long long ldg, void* out, long long ldo, int T, int H, int G, int D, int Vd, int block_size,
+                    float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks, int sink,
+                    float out_scale, int dtype, int flags, atx_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif
