@@ -38,6 +38,7 @@ EXPORTS = [
     "atx_attn_local_prefill", "atx_attn_local_prefill_supported",
     "atx_linear_recurrence_chunked", "atx_linear_recurrence_chunked_supported",
     "atx_embed_rows_scaled", "atx_tanh_norm", "atx_unary_act", "atx_head_prepare", "atx_head_gemm", "atx_attn_window",
+    "atx_attn_window_prefill", "atx_attn_window_prefill_supported",
 ]
 ACT_RELU2 = 0
 ACT_GELU_TANH = 1
@@ -146,6 +147,9 @@ def load() -> C.CDLL:
     lib.atx_head_gemm.argtypes = [vp, i32, i64, i32, i32, vp, i64, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32, i32, i32, vp]
     lib.atx_attn_window.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i64, vp, i64, i32, i32, i32, i32, i32, i32,
                                     f32, f32, i32, i32, vp, vp, i32, f32, i32, i32, vp]
+    lib.atx_attn_window_prefill_supported.argtypes = [i32, i32, i64, i64, i32]
+    lib.atx_attn_window_prefill.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i32, i32, vp, i64, vp, i64, i32, i32,
+                                            i32, i32, i32, f32, f32, i32, i32, vp, vp, i32, f32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

@@ -418,6 +418,28 @@ class Program:
         self.first_mix = cfg.first_mix_layer()
 
     # ------------------------------------------------------------------------------------------------------------------
+    def _attend(self, q: int, kc: int, vc: int, k_row: int, v_row: int, out: int, ldo: int, T: int, n_dec: int, n_pf: int,
+                H: int, G: int, D: int, Vd: int, scale: float, window: int, slopes, sinks, fl: int, st: int) -> int:
+        """Attention of the step's rows over their sequences' pages: prompt portions on the tensor cores where the
+        element type and the sizes have such a kernel; single decoded tokens (and every row otherwise) on the kernel
+        that gives a warp to each (row, head). Returns the launch count."""
+        r, lib, ck, dp, dt = self.r, self.r.lib, self.r._ck, self.r._dp, self.dt
+        sink = 1 if sinks is not None else 0
+        tc = n_pf > 0 and lib.atx_attn_window_prefill_supported(D, Vd, k_row, v_row, dt)
+        rows = n_dec if tc else T
+        n = 0
+        if rows:
+            ck(lib.atx_attn_window(q, kc, vc, k_row, v_row, dp["seq_bt"], r.MB, dp["tok_seq"], dp["pos"], None, 0, out, ldo,
+                                   rows, H, G, D, Vd, r.bs, scale, 0.0, 0, window, slopes, sinks, sink, 1.0, dt, fl, st))
+            n += 1
+        if tc:
+            ck(lib.atx_attn_window_prefill(q, kc, vc, k_row, v_row, dp["seq_bt"] + 4 * n_dec * r.MB, r.MB,
+                                           dp["seq_start"] + 4 * n_dec, dp["seq_count"] + 4 * n_dec,
+                                           dp["seq_pos0"] + 4 * n_dec, n_pf, T - n_dec, None, 0, out, ldo, H, G, D, Vd, r.bs,
+                                           scale, 0.0, 0, window, slopes, sinks, sink, 1.0, dt, fl, st))
+            n += 1
+        return n
+
     def forward(self, T: int, n_dec: int, n_pf: int, n_rows: int) -> int:
         """Issue every kernel of one step on the current stream; returns the launch count. The step's first n_dec
         sequences are single decoded tokens (rows 0 .. n_dec-1), the next n_pf are prompt portions."""
@@ -469,10 +491,8 @@ class Program:
                               save=vf if first else None, mix_src=vf if (mixing and not first) else None, mix=l.vmix,
                               dst_kind=PAGES, dst=vc.data_ptr(), dst_off=0, dst_stride=Vd))
                 ck(lib.atx_head_prepare(proj, ld, sg, 3, dp["pos"], dp["slots"], T, bs, eps, dt, fl, st))
-                ck(lib.atx_attn_window(qb, kc.data_ptr(), vc.data_ptr(), D, Vd, dp["seq_bt"], r.MB, dp["tok_seq"],
-                                       dp["pos"], None, 0, mix, K_o, T, H, G, D, Vd, bs, float(c["scale"]), 0.0, 0,
-                                       window, l.slopes.data_ptr(), l.sinks.data_ptr(), 1, 1.0, dt, fl, st))
-                n += 2
+                n += 1 + self._attend(qb, kc.data_ptr(), vc.data_ptr(), D, Vd, mix, K_o, T, n_dec, n_pf, H, G, D, Vd,
+                                      float(c["scale"]), window, l.slopes.data_ptr(), l.sinks.data_ptr(), fl, st)
             else:
                 H, D, R, Vd, C, Q = c["heads"], c["dim"], c["rot_dim"], c["vdim"], c["kv_rank"], c["q_rank"]
                 rot = c.get("rot") or {}
@@ -493,13 +513,12 @@ class Program:
                 ck(lib.atx_head_prepare(q2, n_q2, sg, 1, dp["pos"], dp["slots"], T, bs, eps, dt, fl, st))
                 ck(lib.atx_head_gemm(q2, 1, n_q2, 0, D + R, l.w_ukt.data_ptr(), D, None, 0, qb, H * (C + R), 0, C + R, T, H,
                                      C, D, dt, fl, st))
-                ck(lib.atx_attn_window(qb, kc.data_ptr(), kc.data_ptr(), C + R, C + R, dp["seq_bt"], r.MB, dp["tok_seq"],
-                                       dp["pos"], None, 0, lat, H * C, T, H, 1, C + R, C, bs, float(c["scale"]), 0.0, 0,
-                                       window, None, None, 0, 1.0, dt, fl, st))
+                n += self._attend(qb, kc.data_ptr(), kc.data_ptr(), C + R, C + R, lat, H * C, T, n_dec, n_pf, H, 1, C + R, C,
+                                  float(c["scale"]), window, None, None, fl, st)
                 # values of the head from its attention output over latents, times the output gate
                 ck(lib.atx_head_gemm(lat, 0, H * C, 0, C, l.w_uv.data_ptr(), C, proj + 4 * (Q + C + R), ld, mix, K_o, 0, Vd,
                                      T, H, Vd, C, dt, fl, st))
-                n += 6
+                n += 5
             lin["o"].run(h, W, T, fl, st, mode=ADD)
             n += 1
             if "up" in lin:

@@ -270,14 +270,19 @@ __device__ __forceinline__ float rcp_approx(float x) {
 
 constexpr int kTcRows = 64, kTcKeys = 64;
 
+// D and VD are the tile's key and value widths; the heads' own sizes d_real <= D and vd_real <= VD (multiples of 8) are
+// run-time values: the columns between are zero in shared memory, so one instance serves every size up to its own.
+// A token's key row has k_row elements and its value row v_row (keys and values may share one page array). window > 0
+// cuts the keys below p - window + 1; slopes[h] (p - j) is taken off the score; sinks[h] is the learned score of the sink.
 template <int D, int VD>
-__global__ void __launch_bounds__(128, (D <= 64 ? 4 : 3))
+__global__ void __launch_bounds__(128, (D <= 64 ? 4 : (D <= 128 ? 3 : 2)))
 attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                      const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
                      const int* __restrict__ seq_start, const int* __restrict__ seq_count,
                      const int* __restrict__ seq_pos0, int n_seqs, const float* __restrict__ gate, long long ldg,
                      __nv_bfloat16* __restrict__ out, long long ldo, int H, int G, int bs, float scale, float softcap,
-                     int chunk, int sink, float out_scale) {
+                     int chunk, int sink, float out_scale, int d_real, int vd_real, long long k_row, long long v_row,
+                     int window, const float* __restrict__ slopes, const float* __restrict__ sinks) {
     constexpr int LQ = D + 8, LV = VD + 8;     // padded rows: ldmatrix without bank conflicts, 16-byte aligned
     extern __shared__ __align__(16) unsigned char smem_raw[];
     static_assert(kTcRows == kTcKeys, "the query tile is staged in a key stage");
@@ -298,13 +303,20 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const long long row0 = seq_start[s] + tile * kTcRows;
     const int nrows = min(kTcRows, seq_count[s] - tile * kTcRows);
     const int p0 = seq_pos0[s] + tile * kTcRows, p1 = p0 + nrows - 1;
-    const int lo = chunk > 0 ? (p0 / chunk) * chunk : 0;
+    auto lower_edge = [&](int p) -> int {   // first key a query at p sees
+        int e = chunk > 0 ? (p / chunk) * chunk : 0;
+        if (window > 0) e = max(e, p - window + 1);
+        return e;
+    };
+    const int lo = lower_edge(p0);
     const int* bt = block_tables + static_cast<long long>(s) * max_blocks;
+    const int dq8 = d_real / 8, dv8 = vd_real / 8;
 
     for (int c = threadIdx.x; c < kTcRows * (D / 8); c += 128) {
         const int r = c / (D / 8), part = c - r * (D / 8);
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < nrows) v = __ldg(reinterpret_cast<const uint4*>(q + ((row0 + r) * H + h) * D + part * 8));
+        if (r < nrows && part < dq8)
+            v = __ldg(reinterpret_cast<const uint4*>(q + ((row0 + r) * H + h) * d_real + part * 8));
         *reinterpret_cast<uint4*>(sQ + r * LQ + part * 8) = v;
     }
     __syncthreads();
@@ -316,20 +328,23 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     float o[VD / 8][4];
 #pragma unroll
     for (int i = 0; i < VD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    constexpr float kLog2e = 1.4426950408889634f;
+    const bool has_sink = sink || sinks;
     float m[2], l[2];
-    m[0] = m[1] = sink ? 0.f : -INFINITY;     // the sink: a key of score 0 without a value
-    l[0] = l[1] = sink ? 1.f : 0.f;
+    // the sink: a key without a value whose score is 0 or a learned number per head (kept in the base-2 domain like the rest)
+    m[0] = m[1] = has_sink ? (sinks ? sinks[h] * kLog2e : 0.f) : -INFINITY;
+    l[0] = l[1] = has_sink ? 1.f : 0.f;
+    const float slope2 = slopes ? slopes[h] * kLog2e : 0.f;
     int pr[2], plo[2];
     pr[0] = p0 + warp * 16 + (lane >> 2);
     pr[1] = pr[0] + 8;
-    plo[0] = chunk > 0 ? (pr[0] / chunk) * chunk : 0;
-    plo[1] = chunk > 0 ? (pr[1] / chunk) * chunk : 0;
+    plo[0] = lower_edge(pr[0]);
+    plo[1] = lower_edge(pr[1]);
     // Scores live in the base-2 domain (s * log2 e), so that every exponential is one ex2. With a cap c:
     // c tanh(x / c) = c - 2c / (1 + exp(2x / c)), one ex2 and one rcp; the constants carry scale and log2 e.
-    constexpr float kLog2e = 1.4426950408889634f;
     const float c_in = softcap > 0.f ? 2.f * scale / softcap * kLog2e : scale * kLog2e;
     const float cap2 = softcap * kLog2e;
-    const int plo_last = chunk > 0 ? ((p0 + warp * 16 + 15) / chunk) * chunk : 0;   // lower edge of this warp's last row
+    const int plo_last = lower_edge(p0 + warp * 16 + 15);   // lower edge of this warp's last row
 
     __syncthreads();   // every warp holds its query fragments: key stage 1 may be filled
     const int bs_shift = (bs & (bs - 1)) == 0 ? __ffs(bs) - 1 : -1;   // pages of 2^n tokens: shift and mask, no division
@@ -340,26 +355,18 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     auto load_tile = [&](int k0, int stage) {
         __nv_bfloat16* dk = sKs + stage * kTcKeys * LQ;
         __nv_bfloat16* dv = sVs + stage * kTcKeys * LV;
-        // rows past the portion become zeros (0 x garbage would not be 0)
-        if constexpr (D == VD) {   // one page lookup per row serves the key and the value
-            for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
-                const int r = c / (D / 8), part = c - r * (D / 8);
-                const int kp = k0 + r;
-                const long long slot = slot_of(min(kp, p1));
-                cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot * D + part * 8, kp <= p1);
-                cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot * VD + part * 8, kp <= p1);
-            }
-        } else {
-            for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
-                const int r = c / (D / 8), part = c - r * (D / 8);
-                const int kp = k0 + r;
-                cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot_of(min(kp, p1)) * D + part * 8, kp <= p1);
-            }
-            for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
-                const int r = c / (VD / 8), part = c - r * (VD / 8);
-                const int kp = k0 + r;
-                cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot_of(min(kp, p1)) * VD + part * 8, kp <= p1);
-            }
+        // rows past the portion and columns past the head's own size become zeros (0 x garbage would not be 0)
+        for (int c = threadIdx.x; c < kTcKeys * (D / 8); c += 128) {
+            const int r = c / (D / 8), part = c - r * (D / 8);
+            const int kp = k0 + r;
+            const bool ok = kp <= p1 && part < dq8;
+            cp_async16_zfill(dk + r * LQ + part * 8, k_cache + slot_of(min(kp, p1)) * k_row + (ok ? part * 8 : 0), ok);
+        }
+        for (int c = threadIdx.x; c < kTcKeys * (VD / 8); c += 128) {
+            const int r = c / (VD / 8), part = c - r * (VD / 8);
+            const int kp = k0 + r;
+            const bool ok = kp <= p1 && part < dv8;
+            cp_async16_zfill(dv + r * LV + part * 8, v_cache + slot_of(min(kp, p1)) * v_row + (ok ? part * 8 : 0), ok);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
@@ -406,6 +413,16 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
             for (int nb = 0; nb < kTcKeys / 8; ++nb) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) sc[nb][e] *= c_in;
+            }
+        }
+        if (slope2 != 0.f) {   // penalty per unit of distance between query and key
+#pragma unroll
+            for (int nb = 0; nb < kTcKeys / 8; ++nb) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int col = k0 + nb * 8 + (lane & 3) * 2 + (e & 1);
+                    sc[nb][e] = fmaf(-slope2, static_cast<float>(pr[e >> 1] - col), sc[nb][e]);
+                }
             }
         }
         if (edge) {
@@ -482,19 +499,25 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         if (r >= nrows) continue;
         float mul = out_scale / l[rr];
         if (gate) mul *= 1.f / (1.f + __expf(-gate[(row0 + r) * ldg + h]));
-        __nv_bfloat16* orow = out + (row0 + r) * ldo + static_cast<long long>(h) * VD + (lane & 3) * 2;
+        __nv_bfloat16* orow = out + (row0 + r) * ldo + static_cast<long long>(h) * vd_real + (lane & 3) * 2;
 #pragma unroll
         for (int nb = 0; nb < VD / 8; ++nb)
-            *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
+            if (nb < dv8) *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
     }
 }
 
+struct AttnTcArgs {
+    const void *q, *k_cache, *v_cache;
+    const int *block_tables, *seq_start, *seq_count, *seq_pos0;
+    const float *gate, *slopes, *sinks;
+    void* out;
+    long long ldg, ldo, k_row, v_row;
+    int max_blocks, n_seqs, max_tiles, H, G, D, Vd, bs, chunk, window, sink, flags;
+    float scale, softcap, out_scale;
+};
+
 template <int D, int VD>
-static int launch_attn_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_tables,
-                          int max_blocks, const int* seq_start, const int* seq_count, const int* seq_pos0, int n_seqs,
-                          int max_tiles, const float* gate, long long ldg, void* out, long long ldo, int H, int G, int bs,
-                          float scale, float softcap, int chunk, int sink, float out_scale, int flags,
-                          cudaStream_t stream) {
+static int launch_attn_tc(const AttnTcArgs& a, cudaStream_t stream) {
     const int smem = 2 * kTcKeys * (D + 8) * 2 + 2 * kTcKeys * (VD + 8) * 2;
     static bool attr_done = false;
     if (!attr_done && smem > 48 * 1024) {
@@ -503,23 +526,28 @@ static int launch_attn_tc(const void* q, const void* k_cache, const void* v_cach
     }
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    cfg.gridDim = dim3(max_tiles, H);
+    cfg.gridDim = dim3(a.max_tiles, a.H);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
-    if (flags & ATX_FLAG_PDL) {
+    if (a.flags & ATX_FLAG_PDL) {
         attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
     }
     using B = __nv_bfloat16;
-    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD>, reinterpret_cast<const B*>(q),
-                                reinterpret_cast<const B*>(k_cache), reinterpret_cast<const B*>(v_cache), block_tables,
-                                max_blocks, seq_start, seq_count, seq_pos0, n_seqs, gate, ldg, reinterpret_cast<B*>(out),
-                                ldo, H, G, bs, scale, softcap, chunk, sink, out_scale));
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD>, reinterpret_cast<const B*>(a.q),
+                                reinterpret_cast<const B*>(a.k_cache), reinterpret_cast<const B*>(a.v_cache),
+                                a.block_tables, a.max_blocks, a.seq_start, a.seq_count, a.seq_pos0, a.n_seqs, a.gate, a.ldg,
+                                reinterpret_cast<B*>(a.out), a.ldo, a.H, a.G, a.bs, a.scale, a.softcap, a.chunk, a.sink,
+                                a.out_scale, a.D, a.Vd, a.k_row, a.v_row, a.window, a.slopes, a.sinks));
     return ATX_OK;
 }
+
+// key width of the smallest instance that holds D (0: none)
+static int tc_key_width(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : (D <= 192 ? 192 : (D <= 256 ? 256 : 0))); }
+static int tc_value_width(int Vd) { return Vd <= 64 ? 64 : (Vd <= 128 ? 128 : 0); }
 
 }  // namespace atx
 
@@ -638,25 +666,64 @@ int atx_attn_local_prefill(const void* q, const void* k_cache, const void* v_cac
                            int total_rows, const float* gate, long long ldg, void* out, long long ldo, int H, int G, int D,
                            int Vd, int block_size, float scale, float softcap, int chunk, int sink, float out_scale,
                            int dtype, int flags, atx_stream_t stream) {
-    ATX_REQUIRE(q && k_cache && v_cache && block_tables && seq_start && seq_count && seq_pos0 && out,
-                "atx_attn_local_prefill: null pointer");
-    ATX_REQUIRE(n_seqs > 0 && total_rows > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0,
-                "atx_attn_local_prefill: bad shape n_seqs=%d rows=%d H=%d G=%d", n_seqs, total_rows, H, G);
     if (!atx_attn_local_prefill_supported(D, Vd, dtype)) {
         set_error("atx_attn_local_prefill: bf16 with head sizes (64, 64) or (128, 128) only; got D=%d Vd=%d dtype=%d", D, Vd,
                   dtype);
         return ATX_ERR_UNSUPPORTED;
     }
-    // every sequence adds at most one partly filled tile
-    const int max_tiles = (total_rows + kTcRows - 1) / kTcRows + n_seqs;
+    return atx_attn_window_prefill(q, k_cache, v_cache, D, Vd, block_tables, max_blocks, seq_start, seq_count, seq_pos0,
+                                   n_seqs, total_rows, gate, ldg, out, ldo, H, G, D, Vd, block_size, scale, softcap, chunk,
+                                   0, nullptr, nullptr, sink, out_scale, dtype, flags, stream);
+}
+
+int atx_attn_window_prefill_supported(int D, int Vd, long long k_row, long long v_row, int dtype) {
+    return dtype == ATX_DT_BF16 && D > 0 && Vd > 0 && D % 8 == 0 && Vd % 8 == 0 && k_row % 8 == 0 && v_row % 8 == 0 &&
+                   tc_key_width(D) && tc_value_width(Vd)
+               ? 1
+               : 0;
+}
+
+int atx_attn_window_prefill(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                            const int* block_tables, int max_blocks, const int* seq_start, const int* seq_count,
+                            const int* seq_pos0, int n_seqs, int total_rows, const float* gate, long long ldg, void* out,
+                            long long ldo, int H, int G, int D, int Vd, int block_size, float scale, float softcap,
+                            int chunk, int window, const float* slopes, const float* sinks, int sink, float out_scale,
+                            int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && seq_start && seq_count && seq_pos0 && out,
+                "atx_attn_window_prefill: null pointer");
+    ATX_REQUIRE(n_seqs > 0 && total_rows > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0 && window >= 0 &&
+                    k_row >= D && v_row >= Vd && ldo % 2 == 0,
+                "atx_attn_window_prefill: bad shape n_seqs=%d rows=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld", n_seqs,
+                total_rows, H, G, k_row, v_row, ldo);
+    if (!atx_attn_window_prefill_supported(D, Vd, k_row, v_row, dtype) ||
+        ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & 3)) {
+        set_error("atx_attn_window_prefill: bf16, 16-byte aligned buffers, head and row sizes in multiples of 8, key size "
+                  "<= 256 and value size <= 128 only; got D=%d Vd=%d k_row=%lld v_row=%lld dtype=%d", D, Vd, k_row, v_row,
+                  dtype);
+        return ATX_ERR_UNSUPPORTED;
+    }
+    AttnTcArgs a = {};
+    a.q = q, a.k_cache = k_cache, a.v_cache = v_cache;
+    a.block_tables = block_tables, a.seq_start = seq_start, a.seq_count = seq_count, a.seq_pos0 = seq_pos0;
+    a.gate = gate, a.slopes = slopes, a.sinks = sinks, a.out = out;
+    a.ldg = ldg, a.ldo = ldo, a.k_row = k_row, a.v_row = v_row;
+    a.max_blocks = max_blocks, a.n_seqs = n_seqs;
+    a.max_tiles = (total_rows + kTcRows - 1) / kTcRows + n_seqs;   // every sequence adds at most one partly filled tile
+    a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.chunk = chunk, a.window = window, a.sink = sink, a.flags = flags;
+    a.scale = scale, a.softcap = softcap, a.out_scale = out_scale;
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    if (D == 64)
-        return launch_attn_tc<64, 64>(q, k_cache, v_cache, block_tables, max_blocks, seq_start, seq_count, seq_pos0, n_seqs,
-                                      max_tiles, gate, ldg, out, ldo, H, G, block_size, scale, softcap, chunk, sink,
-                                      out_scale, flags, st);
-    return launch_attn_tc<128, 128>(q, k_cache, v_cache, block_tables, max_blocks, seq_start, seq_count, seq_pos0, n_seqs,
-                                    max_tiles, gate, ldg, out, ldo, H, G, block_size, scale, softcap, chunk, sink,
-                                    out_scale, flags, st);
+    const int kw = tc_key_width(D), vw = tc_value_width(Vd);
+    if (vw == 64) {
+        if (kw == 64) return launch_attn_tc<64, 64>(a, st);
+        if (kw == 128) return launch_attn_tc<128, 64>(a, st);
+        if (kw == 192) return launch_attn_tc<192, 64>(a, st);
+        return launch_attn_tc<256, 64>(a, st);
+    }
+    if (kw == 64) return launch_attn_tc<64, 128>(a, st);
+    if (kw == 128) return launch_attn_tc<128, 128>(a, st);
+    if (kw == 192) return launch_attn_tc<192, 128>(a, st);
+    return launch_attn_tc<256, 128>(a, st);
 }
 
 }  // extern "C"

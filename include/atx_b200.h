@@ -360,6 +360,17 @@ int atx_attn_window(const void* q, const void* k_cache, const void* v_cache, lon
                     long long ldg, void* out, long long ldo, int T, int H, int G, int D, int Vd, int block_size,
                     float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks, int sink,
                     float out_scale, int dtype, int flags, atx_stream_t stream);
+/* atx_attn_window for prompt portions on the tensor cores (the kernel of atx_attn_local_prefill with the same further
+ * options): bf16, key size up to 256 and value size up to 128, head and row sizes in multiples of 8 elements; sizes
+ * between the kernel's tile widths run on the next wider tile with zero columns. ..._supported() says whether a shape has
+ * this kernel (else use atx_attn_window for those rows too). */
+int atx_attn_window_prefill_supported(int D, int Vd, long long k_row, long long v_row, int dtype);
+int atx_attn_window_prefill(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                            const int* block_tables, int max_blocks, const int* seq_start, const int* seq_count,
+                            const int* seq_pos0, int n_seqs, int total_rows, const float* gate, long long ldg, void* out,
+                            long long ldo, int H, int G, int D, int Vd, int block_size, float scale, float softcap,
+                            int chunk, int window, const float* slopes, const float* sinks, int sink, float out_scale,
+                            int dtype, int flags, atx_stream_t stream);
 
 #ifdef __cplusplus
 }
