@@ -19,6 +19,7 @@ GEMM_STORE_F32 = 0
 GEMM_ADD_F32 = 1
 GEMM_STORE_BF16 = 2
 GEMM_SWIGLU_BF16 = 3
+GEMM_RELU2_BF16 = 4
 FLAG_PDL = 1
 FLAG_ORDERED = 2   # atx_gemm_run ADD_F32, T <= 64: fixed-order split-K (bit-reproducible)
 FLAG_ADD_BF16 = 4  # atx_rmsnorm: the `add` buffer is bf16
@@ -192,7 +193,7 @@ class GemmPlan:
 
     def run(self, out: torch.Tensor, T: int, mode: int, splits: int = 0, flags: int = 0) -> None:
         _dev(out)
-        want = torch.bfloat16 if mode in (GEMM_STORE_BF16, GEMM_SWIGLU_BF16) else torch.float32
+        want = torch.bfloat16 if mode in (GEMM_STORE_BF16, GEMM_SWIGLU_BF16, GEMM_RELU2_BF16) else torch.float32
         cols = self.N // 2 if mode == GEMM_SWIGLU_BF16 else self.N
         assert out.dtype == want and out.dim() == 2 and out.shape[1] >= cols and out.shape[0] >= T
         _check(load().atx_gemm_run(self._h, out.data_ptr(), out.stride(0), T, mode, splits, flags, _stream()))

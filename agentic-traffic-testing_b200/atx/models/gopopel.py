@@ -465,7 +465,9 @@ class Program:
             q2 = proj + 4 * _pad4(T * ld)
             n_q2 = lin["uq"].N if "uq" in lin else 0
             up = q2 + 4 * _pad4(T * n_q2)
-            n_up = lin["up"].N if "up" in lin else 0
+            n_ff = lin["up"].N if "up" in lin else 0
+            fused_act = "up" in lin and lin["up"].plan is not None     # squared ReLU in the GEMM's epilogue (tcgen05 path)
+            n_up = 0 if fused_act else n_ff
             acc = lin["in"].accumulates(T)        # decode-sized steps: the split-K GEMMs add into cleared buffers
             zero_bytes = 0
             if acc:
@@ -523,10 +525,14 @@ class Program:
             n += 1
             if "up" in lin:
                 act = self.act_flat.data_ptr()
-                lin["up"].run(up, n_up, T, fl, st, zeroed=acc)
-                ck(lib.atx_unary_act(up, n_up, act, n_up, T, n_up, _cabi.ACT_RELU2, dt, fl, st))
+                if fused_act:
+                    lin["up"].run(act, n_ff, T, fl, st, mode=_cabi.GEMM_RELU2_BF16)
+                else:
+                    lin["up"].run(up, n_ff, T, fl, st, zeroed=acc)
+                    ck(lib.atx_unary_act(up, n_ff, act, n_ff, T, n_ff, _cabi.ACT_RELU2, dt, fl, st))
+                    n += 1
                 lin["down"].run(h, W, T, fl, st, mode=ADD)
-                n += 3
+                n += 2
             if probe is not None:
                 probe.append(self.h[:T].clone())
         if n_rows:

@@ -175,7 +175,7 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
         mbar_wait(accum_bar, 0);
         tc_fence_after();
         pdl_wait();  // `out` may be the residual stream written by the upstream grid
-        const bool nonlinear = mode == ATX_GEMM_SWIGLU_BF16 || ordered;
+        const bool nonlinear = mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_RELU2_BF16 || ordered;
         if (nonlinear && gridDim.z > 1) {
             // Split-K with a nonlinear epilogue (or with ATX_FLAG_ORDERED, where the order of the additions must
             // not depend on timing): the gridDim.z CTAs of this tile form ONE thread-block
@@ -291,11 +291,16 @@ gemm_wt_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_constant__ 
                     for (int j = 0; j < 16; ++j) part[(c + j) * kBM + warp * 32 + lane] = __uint_as_float(v[j]);
                 } else {
                     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+                    const bool relu2 = mode == ATX_GEMM_RELU2_BF16;   // squared ReLU between the two feed-forward GEMMs
 #pragma unroll
                     for (int j = 0; j < 16; ++j) {
                         const int t = t0 + c + j;
-                        if (t < T)
-                            o[static_cast<long long>(t) * ldo + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                        float a = __uint_as_float(v[j]);
+                        if (relu2) {
+                            a = fmaxf(a, 0.f);
+                            a *= a;
+                        }
+                        if (t < T) o[static_cast<long long>(t) * ldo + n] = __float2bfloat16_rn(a);
                     }
                 }
             }
@@ -536,11 +541,16 @@ gemm_wt_persistent_kernel(const __grid_constant__ CUtensorMap tmW, const __grid_
                             }
                         } else {
                             __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out);
+                            const bool relu2 = mode == ATX_GEMM_RELU2_BF16;
 #pragma unroll
                             for (int j = 0; j < 16; ++j) {
                                 const int t = t0 + c + j;
-                                if (t < T)
-                                    o[static_cast<long long>(t) * ldo + n] = __float2bfloat16_rn(__uint_as_float(v[j]));
+                                float a = __uint_as_float(v[j]);
+                                if (relu2) {
+                                    a = fmaxf(a, 0.f);
+                                    a *= a;
+                                }
+                                if (t < T) o[static_cast<long long>(t) * ldo + n] = __float2bfloat16_rn(a);
                             }
                         }
                     }
@@ -635,7 +645,8 @@ static int launch_gemm(const atx_gemm_plan* p, int ti, void* out, long long ldo,
     // the fused-SwiGLU epilogue parks half a tile in the stage buffers: keep them large enough
     // (a whole fp32 tile when the split-K cluster parks partial sums there)
     const bool ordered = (mode & 0x100) != 0;
-    if ((mode & 0xff) == ATX_GEMM_SWIGLU_BF16 || (mode & 0xff) == ATX_GEMM_ADD_F32) {
+    if ((mode & 0xff) == ATX_GEMM_SWIGLU_BF16 || (mode & 0xff) == ATX_GEMM_ADD_F32 ||
+        ((mode & 0xff) == ATX_GEMM_RELU2_BF16 && zs > 1)) {
         // epilogues that park the tile in the (idle) stage buffers: half a tile for SwiGLU, a whole fp32 tile for the
         // split-K cluster reduction and for the 16-byte adds
         const bool whole = zs > 1 || (mode & 0xff) == ATX_GEMM_ADD_F32;
@@ -656,7 +667,7 @@ static int launch_gemm(const atx_gemm_plan* p, int ti, void* out, long long ldo,
         attr[na].val.programmaticStreamSerializationAllowed = 1;
         ++na;
     }
-    if (((mode & 0xff) == ATX_GEMM_SWIGLU_BF16 || ordered) && zs > 1) {  // the K-splits of one tile are one cluster (DSMEM reduction)
+    if (((mode & 0xff) == ATX_GEMM_SWIGLU_BF16 || (mode & 0xff) == ATX_GEMM_RELU2_BF16 || ordered) && zs > 1) {  // the K-splits of one tile are one cluster (DSMEM reduction)
         attr[na].id = cudaLaunchAttributeClusterDimension;
         attr[na].val.clusterDim.x = 1;
         attr[na].val.clusterDim.y = 1;
@@ -751,7 +762,7 @@ int atx_gemm_run(const atx_gemm_plan* p, void* out, long long ldo, int T, int mo
     cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
     ATX_REQUIRE(p && out, "atx_gemm_run: null pointer");
     ATX_REQUIRE(T > 0 && T <= p->T_cap, "atx_gemm_run: T=%d outside (0, %lld]", T, p->T_cap);
-    ATX_REQUIRE(mode >= ATX_GEMM_STORE_F32 && mode <= ATX_GEMM_SWIGLU_BF16, "atx_gemm_run: bad mode %d", mode);
+    ATX_REQUIRE(mode >= ATX_GEMM_STORE_F32 && mode <= ATX_GEMM_RELU2_BF16, "atx_gemm_run: bad mode %d", mode);
     ATX_REQUIRE(ldo >= (mode == ATX_GEMM_SWIGLU_BF16 ? p->N / 2 : p->N), "atx_gemm_run: ldo=%lld too small for N=%lld", ldo, p->N);
     ATX_REQUIRE(mode != ATX_GEMM_SWIGLU_BF16 || p->N % 128 == 0, "atx_gemm_run: SWIGLU mode needs N %% 128 == 0");
     // ATX_FLAG_ORDERED: the K-splits of an ADD are reduced inside a cluster in a fixed order (as for SwiGLU) and ONE CTA
@@ -765,17 +776,18 @@ int atx_gemm_run(const atx_gemm_plan* p, void* out, long long ldo, int T, int mo
     if (splits <= 0) {
         splits = 1;
         if (mode == ATX_GEMM_ADD_F32) splits = atx_gemm_auto_splits(p->N, p->K, T);
-        if (mode == ATX_GEMM_SWIGLU_BF16 && T <= 64) {  // cluster split-K: a power of two, at most 8 CTAs
+        if ((mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_RELU2_BF16) && T <= 64) {  // cluster split-K: a power of two, at most 8 CTAs
             const int want = atx_gemm_auto_splits(p->N, p->K, T);
             while (splits * 2 <= want && splits * 2 <= 8 && (p->K / kBK) % (splits * 2) == 0) splits *= 2;
         }
     }
-    ATX_REQUIRE(splits == 1 || mode == ATX_GEMM_ADD_F32 || mode == ATX_GEMM_SWIGLU_BF16,
+    const bool act_mode = mode == ATX_GEMM_SWIGLU_BF16 || mode == ATX_GEMM_RELU2_BF16;
+    ATX_REQUIRE(splits == 1 || mode == ATX_GEMM_ADD_F32 || act_mode,
                 "atx_gemm_run: split-K (%d) needs ATX_GEMM_ADD_F32 into a zeroed or residual buffer, or "
-                "ATX_GEMM_SWIGLU_BF16 (cluster reduction)", splits);
-    ATX_REQUIRE(mode != ATX_GEMM_SWIGLU_BF16 || splits == 1 ||
+                "ATX_GEMM_SWIGLU_BF16 / ATX_GEMM_RELU2_BF16 (cluster reduction)", splits);
+    ATX_REQUIRE(!act_mode || splits == 1 ||
                     (T <= 64 && splits <= 8 && (splits & (splits - 1)) == 0 && (p->K / kBK) % splits == 0),
-                "atx_gemm_run: SWIGLU split-K needs T <= 64 and splits in {2,4,8} dividing K/64 (got T=%d splits=%d)",
+                "atx_gemm_run: split-K with an activation needs T <= 64 and splits in {2,4,8} dividing K/64 (got T=%d splits=%d)",
                 T, splits);
     const int pdl = (flags & ATX_FLAG_PDL) ? 1 : 0;
     const int kmode = mode | (ordered ? 0x100 : 0);

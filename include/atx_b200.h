@@ -60,6 +60,9 @@ typedef struct atx_gemm_plan atx_gemm_plan;
  * K/64) runs the splits of a tile as one thread-block cluster and sums them through distributed shared
  * memory in a fixed order: no workspace, no atomics, repeatable bit for bit. */
 #define ATX_GEMM_SWIGLU_BF16 3
+/* out bf16 = max(acc, 0)^2: the activation between the GEMMs of a feed-forward without a gate. Split-K (T <= 64) as for
+ * SwiGLU: the splits of a tile are one cluster, summed in a fixed order before the activation. */
+#define ATX_GEMM_RELU2_BF16 4
 int atx_gemm_plan_create(atx_gemm_plan** plan, const void* W, long long N, long long K, const void* X,
                          long long T_cap, long long ldx);
 void atx_gemm_plan_destroy(atx_gemm_plan* plan);

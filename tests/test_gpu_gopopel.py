@@ -706,3 +706,21 @@ def test_tanh_norm_activation_head_gemm_and_scaled_embedding_match_their_formula
     assert lib.atx_embed_rows_scaled(ids.data_ptr(), td.data_ptr(), out.data_ptr(), 4, W, V, 12.5, dt, 0, _st()) == 0
     torch.cuda.synchronize()
     assert torch.allclose(out.cpu().double(), tab[[3, 49, 0, 7]] * 12.5, rtol=1e-6)
+
+
+@pytest.mark.parametrize("T,N,K", [(5, 256, 512), (64, 200, 1024), (100, 384, 128), (300, 520, 320)])
+def test_gemm_with_the_squared_relu_in_its_epilogue(T, N, K):
+    """Decode-sized steps cut K over a cluster and sum the parts before the activation; prompt-sized steps take the
+    persistent kernel. Operands exactly representable in bf16."""
+    lib, cabi = _lib()
+    g = torch.Generator().manual_seed(T + N)
+    w = (torch.randn(N, K, generator=g) / K ** 0.5).to(torch.bfloat16).to(DEV)
+    x = torch.zeros(max(T, 16), K, dtype=torch.bfloat16, device=DEV)
+    x[:T] = torch.randn(T, K, generator=g).to(torch.bfloat16).to(DEV)
+    out = torch.full((T, N + 8), 3.0, dtype=torch.bfloat16, device=DEV)
+    plan = cabi.GemmPlan(w, x)
+    plan.run(out, T, cabi.GEMM_RELU2_BF16)
+    torch.cuda.synchronize()
+    want = R.relu_squared(x[:T].cpu().double() @ w.cpu().double().T)
+    assert torch.allclose(out[:, :N].cpu().double(), want, atol=2e-2, rtol=1e-2)
+    assert float((out[:, N:].float() - 3.0).abs().max()) == 0.0
