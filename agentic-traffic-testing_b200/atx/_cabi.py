@@ -23,6 +23,7 @@ GEMM_RELU2_BF16 = 4
 FLAG_PDL = 1
 FLAG_ORDERED = 2   # atx_gemm_run ADD_F32, T <= 64: fixed-order split-K (bit-reproducible)
 FLAG_ADD_BF16 = 4  # atx_rmsnorm: the `add` buffer is bf16
+FLAG_HEAD_GEMM_FMA = 8   # atx_head_gemm: bf16 on the FMA pipe instead of the tensor cores
 DT_BF16 = 0        # element type of weights / GEMM inputs / KV pages in the calls that take one
 DT_F32 = 1
 
@@ -40,6 +41,7 @@ EXPORTS = [
     "atx_linear_recurrence_chunked", "atx_linear_recurrence_chunked_supported",
     "atx_embed_rows_scaled", "atx_tanh_norm", "atx_unary_act", "atx_head_prepare", "atx_head_gemm", "atx_attn_window",
     "atx_attn_window_prefill", "atx_attn_window_prefill_supported",
+    "atx_attn_window_decode", "atx_attn_window_decode_supported", "atx_attn_window_decode_workspace_bytes",
 ]
 ACT_RELU2 = 0
 ACT_GELU_TANH = 1
@@ -151,6 +153,11 @@ def load() -> C.CDLL:
     lib.atx_attn_window_prefill_supported.argtypes = [i32, i32, i64, i64, i32]
     lib.atx_attn_window_prefill.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i32, i32, vp, i64, vp, i64, i32, i32,
                                             i32, i32, i32, f32, f32, i32, i32, vp, vp, i32, f32, i32, i32, vp]
+    lib.atx_attn_window_decode_supported.argtypes = [i32, i32, i32, i32, i64, i64, i32]
+    lib.atx_attn_window_decode_workspace_bytes.argtypes = [i32, i32, i32, i32]
+    lib.atx_attn_window_decode_workspace_bytes.restype = i64
+    lib.atx_attn_window_decode.argtypes = [vp, vp, vp, i64, i64, vp, i32, vp, vp, vp, i64, vp, i64, vp, i64, i32, i32, i32,
+                                           i32, i32, i32, i32, f32, f32, i32, i32, vp, vp, i32, f32, i32, i32, vp]
     for name in EXPORTS:  # fail at load time, not at first use, if the build is stale
         getattr(lib, name)
     _lib = lib

@@ -152,6 +152,17 @@ class Config:
         return n
 
 
+    def decode_kv_bytes(self, ctx: int, elem: int = 2) -> int:
+        """Page bytes one decoded token at context length ctx reads: every layer at most its window."""
+        n = 0
+        for l in self.layers:
+            c = l["mixer"]
+            keys = min(ctx, int((c.get("mask") or {}).get("size", 0) or ctx))
+            row = c["kv_heads"] * (c["dim"] + c["vdim"]) if l["type"] == "attention" else c["kv_rank"] + c["rot_dim"]
+            n += keys * row * elem
+        return n
+
+
 def named_shape(name: str) -> Optional[Config]:
     """`random:gopopel-<size>`: shapes whose layers resemble a real model's, for benchmarks (no checkpoint exists).
     `gopopel-8b` / `gopopel-1b` have the width, feed-forward size, vocabulary and depth of the Llama 8B / 1B shapes;
@@ -166,7 +177,7 @@ def named_shape(name: str) -> Optional[Config]:
     heads = W // hd
     ffn = {"ff": F, "kind": "dense"}
     lat = {"type": "latent_attention", "mlp": ffn,
-           "mixer": {"dim": hd, "heads": heads, "kv_rank": W // 8, "q_rank": W // 4 * 3 // 2, "rot_dim": 64,
+           "mixer": {"dim": hd, "heads": heads, "kv_rank": 128, "q_rank": W * 3 // 8, "rot_dim": 64,
                      "rot": {"base": 10000.0, "dims": 64}, "mask": {"size": 4096}, "scale": (hd + 64) ** -0.5,
                      "vdim": hd}}
     att = {"type": "attention", "mlp": ffn,
@@ -416,6 +427,11 @@ class Program:
                 if key[1] and key not in self.rot:
                     self.rot[key] = rotation_table(key[0], key[1], e.max_model_len, dev)
         self.first_mix = cfg.first_mix_layer()
+        # scratch of the decode attention's key slices: [tokens, heads, slices, value width + 2] fp32
+        self.max_splits = 16
+        self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
+        h_max = max(spec["mixer"]["heads"] for spec in cfg.layers)
+        self.split_ws = torch.zeros(max(2, r.Smax * h_max * self.max_splits * (128 + 2)), dtype=f32, device=dev)
 
     # ------------------------------------------------------------------------------------------------------------------
     def _attend(self, q: int, kc: int, vc: int, k_row: int, v_row: int, out: int, ldo: int, T: int, n_dec: int, n_pf: int,
@@ -428,7 +444,18 @@ class Program:
         tc = n_pf > 0 and lib.atx_attn_window_prefill_supported(D, Vd, k_row, v_row, dt)
         rows = n_dec if tc else T
         n = 0
-        if rows:
+        if rows and rows == n_dec and lib.atx_attn_window_decode_supported(H, G, D, Vd, k_row, v_row, dt):
+            # decoded tokens: the heads of a key/value group as the rows of a tensor-core tile, the keys cut into slices
+            # (as many as fill the GPU about twice, by the longest span a query of this layer can see: a fixed number per
+            # layer and batch size, so a captured graph stays valid)
+            keys = min(window or r.e.max_model_len, r.e.max_model_len)
+            splits = max(1, min((keys + 63) // 64, self.max_splits, -(-2 * self.sms // (rows * G))))
+            ws = self.split_ws
+            ck(lib.atx_attn_window_decode(q, kc, vc, k_row, v_row, dp["seq_bt"], r.MB, dp["tok_seq"], dp["pos"], None, 0, out,
+                                          ldo, ws.data_ptr(), ws.numel() * 4, splits, rows, H, G, D, Vd, r.bs, scale, 0.0, 0,
+                                          window, slopes, sinks, sink, 1.0, dt, fl, st))
+            n += 2 if splits > 1 else 1
+        elif rows:
             ck(lib.atx_attn_window(q, kc, vc, k_row, v_row, dp["seq_bt"], r.MB, dp["tok_seq"], dp["pos"], None, 0, out, ldo,
                                    rows, H, G, D, Vd, r.bs, scale, 0.0, 0, window, slopes, sinks, sink, 1.0, dt, fl, st))
             n += 1

@@ -274,7 +274,13 @@ constexpr int kTcRows = 64, kTcKeys = 64;
 // run-time values: the columns between are zero in shared memory, so one instance serves every size up to its own.
 // A token's key row has k_row elements and its value row v_row (keys and values may share one page array). window > 0
 // cuts the keys below p - window + 1; slopes[h] (p - j) is taken off the score; sinks[h] is the learned score of the sink.
-template <int D, int VD>
+//
+// DEC: the decode form of the same kernel. A CTA takes ONE token, one key/value head and one slice of the keys; the tile's
+// rows are the query heads that share that key/value head (at most 64), all at the token's position, each with its own
+// slope and sink, so K and V are read once for the whole group. Slices (gridDim.z) write unnormalised partial outputs
+// with their running maximum and sum to `ws` and attn_split_merge_kernel folds them; the sink counts in slice 0 only.
+// Rows are listed by tok_seq / positions (one entry per token) instead of (first row, rows, first position) triples.
+template <int D, int VD, bool DEC>
 __global__ void __launch_bounds__(128, (D <= 64 ? 4 : (D <= 128 ? 3 : 2)))
 attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                      const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_tables, int max_blocks,
@@ -282,7 +288,8 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                      const int* __restrict__ seq_pos0, int n_seqs, const float* __restrict__ gate, long long ldg,
                      __nv_bfloat16* __restrict__ out, long long ldo, int H, int G, int bs, float scale, float softcap,
                      int chunk, int sink, float out_scale, int d_real, int vd_real, long long k_row, long long v_row,
-                     int window, const float* __restrict__ slopes, const float* __restrict__ sinks) {
+                     int window, const float* __restrict__ slopes, const float* __restrict__ sinks,
+                     const int* __restrict__ tok_seq, const int* __restrict__ positions, float* __restrict__ ws) {
     constexpr int LQ = D + 8, LV = VD + 8;     // padded rows: ldmatrix without bank conflicts, 16-byte aligned
     extern __shared__ __align__(16) unsigned char smem_raw[];
     static_assert(kTcRows == kTcKeys, "the query tile is staged in a key stage");
@@ -292,17 +299,32 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     pdl_launch_dependents();
     pdl_wait();
     int tile = gridDim.x - 1 - blockIdx.x, s = 0;   // later tiles see more keys: the heaviest start first
-    for (; s < n_seqs; ++s) {
-        const int nt = (seq_count[s] + kTcRows - 1) / kTcRows;
-        if (tile < nt) break;
-        tile -= nt;
+    const int group = H / G;
+    int h, g, nrows, p0, p1;
+    long long row0;
+    if constexpr (DEC) {
+        row0 = blockIdx.x;                 // the token
+        s = tok_seq[row0];
+        if (s < 0) return;                 // padded row
+        g = blockIdx.y;
+        h = g * group;                     // first head of the group; row r of the tile is head h + r
+        nrows = group;
+        p0 = p1 = positions[row0];
+    } else {
+        for (; s < n_seqs; ++s) {
+            const int nt = (seq_count[s] + kTcRows - 1) / kTcRows;
+            if (tile < nt) break;
+            tile -= nt;
+        }
+        if (s >= n_seqs) return;
+        h = blockIdx.y;
+        g = h / group;
+        row0 = seq_start[s] + tile * kTcRows;
+        nrows = min(kTcRows, seq_count[s] - tile * kTcRows);
+        p0 = seq_pos0[s] + tile * kTcRows;
+        p1 = p0 + nrows - 1;
     }
-    if (s >= n_seqs) return;
-    const int h = blockIdx.y, g = h / (H / G);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const long long row0 = seq_start[s] + tile * kTcRows;
-    const int nrows = min(kTcRows, seq_count[s] - tile * kTcRows);
-    const int p0 = seq_pos0[s] + tile * kTcRows, p1 = p0 + nrows - 1;
     auto lower_edge = [&](int p) -> int {   // first key a query at p sees
         int e = chunk > 0 ? (p / chunk) * chunk : 0;
         if (window > 0) e = max(e, p - window + 1);
@@ -315,8 +337,10 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     for (int c = threadIdx.x; c < kTcRows * (D / 8); c += 128) {
         const int r = c / (D / 8), part = c - r * (D / 8);
         uint4 v = make_uint4(0, 0, 0, 0);
-        if (r < nrows && part < dq8)
-            v = __ldg(reinterpret_cast<const uint4*>(q + ((row0 + r) * H + h) * d_real + part * 8));
+        if (r < nrows && part < dq8) {
+            const long long qrow = DEC ? row0 * H + h + r : (row0 + r) * H + h;
+            v = __ldg(reinterpret_cast<const uint4*>(q + qrow * d_real + part * 8));
+        }
         *reinterpret_cast<uint4*>(sQ + r * LQ + part * 8) = v;
     }
     __syncthreads();
@@ -332,19 +356,26 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     const bool has_sink = sink || sinks;
     float m[2], l[2];
     // the sink: a key without a value whose score is 0 or a learned number per head (kept in the base-2 domain like the rest)
-    m[0] = m[1] = has_sink ? (sinks ? sinks[h] * kLog2e : 0.f) : -INFINITY;
-    l[0] = l[1] = has_sink ? 1.f : 0.f;
-    const float slope2 = slopes ? slopes[h] * kLog2e : 0.f;
+    float slope2[2];
     int pr[2], plo[2];
-    pr[0] = p0 + warp * 16 + (lane >> 2);
-    pr[1] = pr[0] + 8;
-    plo[0] = lower_edge(pr[0]);
-    plo[1] = lower_edge(pr[1]);
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int r = warp * 16 + (lane >> 2) + 8 * rr;
+        const int hr = DEC ? h + min(r, group - 1) : h;          // the row's head
+        const bool sink_here = has_sink && (!DEC || blockIdx.z == 0);   // the sink counts once: in the first slice
+        m[rr] = sink_here ? (sinks ? sinks[hr] * kLog2e : 0.f) : -INFINITY;
+        l[rr] = sink_here ? 1.f : 0.f;
+        slope2[rr] = slopes ? slopes[hr] * kLog2e : 0.f;
+        pr[rr] = DEC ? p0 : p0 + r;
+        plo[rr] = lower_edge(pr[rr]);
+    }
     // Scores live in the base-2 domain (s * log2 e), so that every exponential is one ex2. With a cap c:
     // c tanh(x / c) = c - 2c / (1 + exp(2x / c)), one ex2 and one rcp; the constants carry scale and log2 e.
     const float c_in = softcap > 0.f ? 2.f * scale / softcap * kLog2e : scale * kLog2e;
     const float cap2 = softcap * kLog2e;
-    const int plo_last = lower_edge(p0 + warp * 16 + 15);   // lower edge of this warp's last row
+    const int plo_last = DEC ? lo : lower_edge(p0 + warp * 16 + 15);   // lower edge of this warp's last row
+    const int last_row_pos = DEC ? p0 : p0 + warp * 16 + 15, first_row_pos = DEC ? p0 : p0 + warp * 16;
+    const bool warp_has_rows = warp * 16 < nrows;
 
     __syncthreads();   // every warp holds its query fragments: key stage 1 may be filled
     const int bs_shift = (bs & (bs - 1)) == 0 ? __ffs(bs) - 1 : -1;   // pages of 2^n tokens: shift and mask, no division
@@ -370,9 +401,14 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
     };
-    const int n_tiles = (p1 - lo) / kTcKeys + 1;
-    load_tile(lo, 0);
-    for (int it = 0; it < n_tiles; ++it) {
+    int n_tiles = (p1 - lo) / kTcKeys + 1, it_first = 0;
+    if constexpr (DEC) {   // this slice's share of the tiles
+        const int per = (n_tiles + static_cast<int>(gridDim.z) - 1) / static_cast<int>(gridDim.z);
+        it_first = min(n_tiles, static_cast<int>(blockIdx.z) * per);
+        n_tiles = min(n_tiles, it_first + per);
+    }
+    if (it_first < n_tiles) load_tile(lo + it_first * kTcKeys, it_first & 1);
+    for (int it = it_first; it < n_tiles; ++it) {
         const int k0 = lo + it * kTcKeys;
         if (it + 1 < n_tiles) {
             load_tile(k0 + kTcKeys, (it + 1) & 1);
@@ -383,7 +419,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         __syncthreads();
         const __nv_bfloat16* sK = sKs + (it & 1) * kTcKeys * LQ;
         const __nv_bfloat16* sV = sVs + (it & 1) * kTcKeys * LV;
-        if (k0 <= p0 + warp * 16 + 15) {   // else every key of the tile lies after this warp's rows (warp-uniform)
+        if (k0 <= last_row_pos && warp_has_rows) {   // else every key of the tile lies after this warp's rows, or the warp has none (warp-uniform)
         float sc[kTcKeys / 8][4];
 #pragma unroll
         for (int i = 0; i < kTcKeys / 8; ++i) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.f;
@@ -400,7 +436,7 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
         }
         float mx[2] = {-INFINITY, -INFINITY};
         // only tiles that reach past the warp's first row or start before its last row's block need the mask
-        const bool edge = k0 + kTcKeys - 1 > p0 + warp * 16 || k0 < plo_last;
+        const bool edge = k0 + kTcKeys - 1 > first_row_pos || k0 < plo_last;
         if (softcap > 0.f) {
 #pragma unroll
             for (int nb = 0; nb < kTcKeys / 8; ++nb) {
@@ -415,13 +451,13 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
                 for (int e = 0; e < 4; ++e) sc[nb][e] *= c_in;
             }
         }
-        if (slope2 != 0.f) {   // penalty per unit of distance between query and key
+        if (slopes) {   // penalty per unit of distance between query and key
 #pragma unroll
             for (int nb = 0; nb < kTcKeys / 8; ++nb) {
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
                     const int col = k0 + nb * 8 + (lane & 3) * 2 + (e & 1);
-                    sc[nb][e] = fmaf(-slope2, static_cast<float>(pr[e >> 1] - col), sc[nb][e]);
+                    sc[nb][e] = fmaf(-slope2[e >> 1], static_cast<float>(pr[e >> 1] - col), sc[nb][e]);
                 }
             }
         }
@@ -497,12 +533,63 @@ attn_local_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* _
     for (int rr = 0; rr < 2; ++rr) {
         const int r = warp * 16 + (lane >> 2) + 8 * rr;
         if (r >= nrows) continue;
+        if constexpr (DEC) {
+            if (gridDim.z > 1) {   // partial result of this slice: [VD outputs | maximum | sum] per (token, head, slice)
+                float* w = ws + ((row0 * H + h + r) * gridDim.z + blockIdx.z) * (VD + 2);
+#pragma unroll
+                for (int nb = 0; nb < VD / 8; ++nb)
+                    *reinterpret_cast<float2*>(w + nb * 8 + (lane & 3) * 2) = make_float2(o[nb][2 * rr], o[nb][2 * rr + 1]);
+                if ((lane & 3) == 0) *reinterpret_cast<float2*>(w + VD) = make_float2(m[rr], l[rr]);
+                continue;
+            }
+            float mul = out_scale / l[rr];
+            if (gate) mul *= 1.f / (1.f + __expf(-gate[row0 * ldg + h + r]));
+            __nv_bfloat16* orow = out + row0 * ldo + static_cast<long long>(h + r) * vd_real + (lane & 3) * 2;
+#pragma unroll
+            for (int nb = 0; nb < VD / 8; ++nb)
+                if (nb < dv8) *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
+            continue;
+        }
         float mul = out_scale / l[rr];
         if (gate) mul *= 1.f / (1.f + __expf(-gate[(row0 + r) * ldg + h]));
         __nv_bfloat16* orow = out + (row0 + r) * ldo + static_cast<long long>(h) * vd_real + (lane & 3) * 2;
 #pragma unroll
         for (int nb = 0; nb < VD / 8; ++nb)
             if (nb < dv8) *reinterpret_cast<uint32_t*>(orow + nb * 8) = pack_bf16(o[nb][2 * rr] * mul, o[nb][2 * rr + 1] * mul);
+    }
+}
+
+// key width of the smallest instance that holds D (0: none)
+static int tc_key_width(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : (D <= 192 ? 192 : (D <= 256 ? 256 : 0))); }
+static int tc_value_width(int Vd) { return Vd <= 64 ? 64 : (Vd <= 128 ? 128 : 0); }
+
+// Folds the slices of the decode form: out = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M = max_s m_s (base-2 domain).
+__global__ void __launch_bounds__(128)
+attn_split_merge_kernel(const float* __restrict__ ws, int splits, int vd_pad, int vd_real, const int* __restrict__ tok_seq,
+                        const float* __restrict__ gate, long long ldg, __nv_bfloat16* __restrict__ out, long long ldo, int H,
+                        float out_scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long t = blockIdx.x;
+    const int h = blockIdx.y;
+    if (tok_seq[t] < 0) return;
+    const float* w = ws + (t * H + h) * splits * (vd_pad + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, w[s * (vd_pad + 2) + vd_pad]);
+    float den = 0.f;
+    for (int s = 0; s < splits; ++s) {
+        const float ms = w[s * (vd_pad + 2) + vd_pad];
+        if (ms != -INFINITY) den += w[s * (vd_pad + 2) + vd_pad + 1] * ex2_approx(ms - M);
+    }
+    float mul = out_scale / den;
+    if (gate) mul *= 1.f / (1.f + __expf(-gate[t * ldg + h]));
+    for (int d = threadIdx.x; d < vd_real; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = w[s * (vd_pad + 2) + vd_pad];
+            if (ms != -INFINITY) acc = fmaf(w[s * (vd_pad + 2) + d], ex2_approx(ms - M), acc);
+        }
+        out[t * ldo + static_cast<long long>(h) * vd_real + d] = __float2bfloat16_rn(acc * mul);
     }
 }
 
@@ -514,19 +601,23 @@ struct AttnTcArgs {
     long long ldg, ldo, k_row, v_row;
     int max_blocks, n_seqs, max_tiles, H, G, D, Vd, bs, chunk, window, sink, flags;
     float scale, softcap, out_scale;
+    // decode form: rows listed by tok_seq / positions, slices of the keys, scratch for their partial results
+    const int *tok_seq, *positions;
+    float* ws;
+    int splits;
 };
 
-template <int D, int VD>
+template <int D, int VD, bool DEC>
 static int launch_attn_tc(const AttnTcArgs& a, cudaStream_t stream) {
     const int smem = 2 * kTcKeys * (D + 8) * 2 + 2 * kTcKeys * (VD + 8) * 2;
     static bool attr_done = false;
     if (!attr_done && smem > 48 * 1024) {
-        ATX_CUDA(cudaFuncSetAttribute(attn_local_tc_kernel<D, VD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+        ATX_CUDA(cudaFuncSetAttribute(attn_local_tc_kernel<D, VD, DEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
         attr_done = true;
     }
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    cfg.gridDim = dim3(a.max_tiles, a.H);
+    cfg.gridDim = DEC ? dim3(a.n_seqs, a.G, a.splits) : dim3(a.max_tiles, a.H);
     cfg.blockDim = dim3(128);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = stream;
@@ -537,17 +628,35 @@ static int launch_attn_tc(const AttnTcArgs& a, cudaStream_t stream) {
         cfg.numAttrs = 1;
     }
     using B = __nv_bfloat16;
-    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD>, reinterpret_cast<const B*>(a.q),
+    ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_local_tc_kernel<D, VD, DEC>, reinterpret_cast<const B*>(a.q),
                                 reinterpret_cast<const B*>(a.k_cache), reinterpret_cast<const B*>(a.v_cache),
                                 a.block_tables, a.max_blocks, a.seq_start, a.seq_count, a.seq_pos0, a.n_seqs, a.gate, a.ldg,
                                 reinterpret_cast<B*>(a.out), a.ldo, a.H, a.G, a.bs, a.scale, a.softcap, a.chunk, a.sink,
-                                a.out_scale, a.D, a.Vd, a.k_row, a.v_row, a.window, a.slopes, a.sinks));
+                                a.out_scale, a.D, a.Vd, a.k_row, a.v_row, a.window, a.slopes, a.sinks, a.tok_seq, a.positions,
+                                a.ws));
+    if (DEC && a.splits > 1) {
+        cfg.gridDim = dim3(a.n_seqs, a.H);
+        cfg.dynamicSmemBytes = 0;
+        ATX_CUDA(cudaLaunchKernelEx(&cfg, attn_split_merge_kernel, const_cast<const float*>(a.ws), a.splits, VD, a.Vd,
+                                    a.tok_seq, a.gate, a.ldg, reinterpret_cast<B*>(a.out), a.ldo, a.H, a.out_scale));
+    }
     return ATX_OK;
 }
 
-// key width of the smallest instance that holds D (0: none)
-static int tc_key_width(int D) { return D <= 64 ? 64 : (D <= 128 ? 128 : (D <= 192 ? 192 : (D <= 256 ? 256 : 0))); }
-static int tc_value_width(int Vd) { return Vd <= 64 ? 64 : (Vd <= 128 ? 128 : 0); }
+template <bool DEC>
+static int dispatch_attn_tc(const AttnTcArgs& a, cudaStream_t st) {
+    const int kw = tc_key_width(a.D), vw = tc_value_width(a.Vd);
+    if (vw == 64) {
+        if (kw == 64) return launch_attn_tc<64, 64, DEC>(a, st);
+        if (kw == 128) return launch_attn_tc<128, 64, DEC>(a, st);
+        if (kw == 192) return launch_attn_tc<192, 64, DEC>(a, st);
+        return launch_attn_tc<256, 64, DEC>(a, st);
+    }
+    if (kw == 64) return launch_attn_tc<64, 128, DEC>(a, st);
+    if (kw == 128) return launch_attn_tc<128, 128, DEC>(a, st);
+    if (kw == 192) return launch_attn_tc<192, 128, DEC>(a, st);
+    return launch_attn_tc<256, 128, DEC>(a, st);
+}
 
 }  // namespace atx
 
@@ -712,18 +821,51 @@ int atx_attn_window_prefill(const void* q, const void* k_cache, const void* v_ca
     a.max_tiles = (total_rows + kTcRows - 1) / kTcRows + n_seqs;   // every sequence adds at most one partly filled tile
     a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.chunk = chunk, a.window = window, a.sink = sink, a.flags = flags;
     a.scale = scale, a.softcap = softcap, a.out_scale = out_scale;
-    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-    const int kw = tc_key_width(D), vw = tc_value_width(Vd);
-    if (vw == 64) {
-        if (kw == 64) return launch_attn_tc<64, 64>(a, st);
-        if (kw == 128) return launch_attn_tc<128, 64>(a, st);
-        if (kw == 192) return launch_attn_tc<192, 64>(a, st);
-        return launch_attn_tc<256, 64>(a, st);
+    return dispatch_attn_tc<false>(a, reinterpret_cast<cudaStream_t>(stream));
+}
+
+int atx_attn_window_decode_supported(int H, int G, int D, int Vd, long long k_row, long long v_row, int dtype) {
+    return G > 0 && H % G == 0 && H / G <= kTcRows && atx_attn_window_prefill_supported(D, Vd, k_row, v_row, dtype) ? 1 : 0;
+}
+
+long long atx_attn_window_decode_workspace_bytes(int T, int H, int Vd, int splits) {
+    const int vw = tc_value_width(Vd);
+    if (T <= 0 || H <= 0 || splits <= 1 || !vw) return 0;
+    return static_cast<long long>(T) * H * splits * (vw + 2) * 4;
+}
+
+int atx_attn_window_decode(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                           const int* block_tables, int max_blocks, const int* tok_seq, const int* positions,
+                           const float* gate, long long ldg, void* out, long long ldo, void* workspace,
+                           long long workspace_bytes, int splits, int T, int H, int G, int D, int Vd, int block_size,
+                           float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks,
+                           int sink, float out_scale, int dtype, int flags, atx_stream_t stream) {
+    ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_window_decode: null pointer");
+    ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0 && window >= 0 && k_row >= D &&
+                    v_row >= Vd && ldo % 2 == 0 && splits >= 1 && splits <= 65535 && G <= 65535,
+                "atx_attn_window_decode: bad shape T=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld splits=%d", T, H, G, k_row,
+                v_row, ldo, splits);
+    if (!atx_attn_window_decode_supported(H, G, D, Vd, k_row, v_row, dtype) ||
+        ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k_cache) | reinterpret_cast<uintptr_t>(v_cache)) & 15) ||
+        (reinterpret_cast<uintptr_t>(out) & 3)) {
+        set_error("atx_attn_window_decode: bf16, 16-byte aligned buffers, sizes in multiples of 8, key size <= 256, value "
+                  "size <= 128, at most 64 query heads per key/value head; got H=%d G=%d D=%d Vd=%d dtype=%d", H, G, D, Vd,
+                  dtype);
+        return ATX_ERR_UNSUPPORTED;
     }
-    if (kw == 64) return launch_attn_tc<64, 128>(a, st);
-    if (kw == 128) return launch_attn_tc<128, 128>(a, st);
-    if (kw == 192) return launch_attn_tc<192, 128>(a, st);
-    return launch_attn_tc<256, 128>(a, st);
+    ATX_REQUIRE(workspace_bytes >= atx_attn_window_decode_workspace_bytes(T, H, Vd, splits) &&
+                    (splits == 1 || (workspace && (reinterpret_cast<uintptr_t>(workspace) & 7) == 0)),
+                "atx_attn_window_decode: %d slices need %lld bytes of scratch (8-byte aligned), got %lld", splits,
+                atx_attn_window_decode_workspace_bytes(T, H, Vd, splits), workspace_bytes);
+    AttnTcArgs a = {};
+    a.q = q, a.k_cache = k_cache, a.v_cache = v_cache;
+    a.block_tables = block_tables, a.tok_seq = tok_seq, a.positions = positions;
+    a.gate = gate, a.slopes = slopes, a.sinks = sinks, a.out = out;
+    a.ldg = ldg, a.ldo = ldo, a.k_row = k_row, a.v_row = v_row;
+    a.max_blocks = max_blocks, a.n_seqs = T, a.splits = splits, a.ws = reinterpret_cast<float*>(workspace);
+    a.H = H, a.G = G, a.D = D, a.Vd = Vd, a.bs = block_size, a.chunk = chunk, a.window = window, a.sink = sink, a.flags = flags;
+    a.scale = scale, a.softcap = softcap, a.out_scale = out_scale;
+    return dispatch_attn_tc<true>(a, reinterpret_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -251,6 +251,69 @@ head_gemm_kernel(const XI* __restrict__ X, long long ldx, int x_off, int xs, con
     }
 }
 
+// The same product on the tensor cores (bf16 operands, fp32 accumulation): 64 rows x 64 outputs of one head per CTA, a
+// warp owns 16 rows; X (fp32 or bf16) and W are staged as bf16 in chunks of 64 reduction elements, zero past the edges.
+constexpr int kHT = 64, kHKC = 64, kHLD = kHKC + 8;
+
+template <typename XI>
+__global__ void __launch_bounds__(128)
+head_gemm_tc_kernel(const XI* __restrict__ X, long long ldx, int x_off, int xs, const __nv_bfloat16* __restrict__ W,
+                    long long ldw, const float* __restrict__ gate, long long ldg, __nv_bfloat16* __restrict__ out,
+                    long long ldo, int o_off, int os, int T, int N, int K) {
+    __shared__ __align__(16) __nv_bfloat16 sx[kHT * kHLD];
+    __shared__ __align__(16) __nv_bfloat16 sw[kHT * kHLD];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int h = blockIdx.z;
+    const int t0 = blockIdx.y * kHT, n0 = blockIdx.x * kHT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const XI* Xh = X + x_off + static_cast<long long>(h) * xs;
+    const __nv_bfloat16* Wh = W + static_cast<long long>(h) * N * ldw;
+    float acc[kHT / 8][4];
+#pragma unroll
+    for (int i = 0; i < kHT / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    for (int k0 = 0; k0 < K; k0 += kHKC) {
+        for (int e = threadIdx.x; e < kHT * kHKC; e += 128) {
+            const int r = e / kHKC, kk = e - r * kHKC;
+            const int t = t0 + r, n = n0 + r, k = k0 + kk;
+            const float xv = (t < T && k < K) ? hld(Xh, static_cast<long long>(t) * ldx + k) : 0.f;
+            sx[r * kHLD + kk] = __float2bfloat16_rn(xv);
+            sw[r * kHLD + kk] = (n < N && k < K) ? Wh[static_cast<long long>(n) * ldw + k] : __float2bfloat16_rn(0.f);
+        }
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < kHKC / 16; ++ks) {
+            uint32_t a[4];
+            ldsm_x4(smem_u32(sx + (warp * 16 + (lane & 15)) * kHLD + ks * 16 + (lane >> 4) * 8), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int nb2 = 0; nb2 < kHT / 16; ++nb2) {
+                uint32_t b0, b1, b2, b3;
+                ldsm_x4(smem_u32(sw + (nb2 * 16 + (lane >> 4) * 8 + (lane & 7)) * kHLD + ks * 16 + ((lane >> 3) & 1) * 8), b0,
+                        b1, b2, b3);
+                mma_bf16(acc[2 * nb2], a, b0, b1);
+                mma_bf16(acc[2 * nb2 + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int rr = 0; rr < 2; ++rr) {
+        const int t = t0 + warp * 16 + (lane >> 2) + 8 * rr;
+        if (t >= T) continue;
+#pragma unroll
+        for (int nb = 0; nb < kHT / 8; ++nb) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int n = n0 + nb * 8 + (lane & 3) * 2 + e;
+                if (n >= N) continue;
+                float v = acc[nb][2 * rr + e];
+                if (gate) v *= 1.f / (1.f + __expf(-gate[static_cast<long long>(t) * ldg + static_cast<long long>(h) * N + n]));
+                out[static_cast<long long>(t) * ldo + o_off + static_cast<long long>(h) * os + n] = __float2bfloat16_rn(v);
+            }
+        }
+    }
+}
+
 }  // namespace atx
 
 using namespace atx;
@@ -344,6 +407,20 @@ int atx_head_gemm(const void* X, int x_f32, long long ldx, int x_off, int x_head
     cfg.blockDim = dim3(256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl_attr(cfg, attr, flags);
+    if (dtype == ATX_DT_BF16 && !(flags & ATX_FLAG_HEAD_GEMM_FMA)) {   // bf16: the tensor cores
+        using B = __nv_bfloat16;
+        cfg.gridDim = dim3((N + kHT - 1) / kHT, (T + kHT - 1) / kHT, heads);
+        cfg.blockDim = dim3(128);
+        if (x_f32)
+            ATX_CUDA(cudaLaunchKernelEx(&cfg, head_gemm_tc_kernel<float>, reinterpret_cast<const float*>(X), ldx, x_off,
+                                        x_head_stride, reinterpret_cast<const B*>(W), ldw, gate, ldg,
+                                        reinterpret_cast<B*>(out), ldo, o_off, o_head_stride, T, N, K));
+        else
+            ATX_CUDA(cudaLaunchKernelEx(&cfg, head_gemm_tc_kernel<B>, reinterpret_cast<const B*>(X), ldx, x_off,
+                                        x_head_stride, reinterpret_cast<const B*>(W), ldw, gate, ldg,
+                                        reinterpret_cast<B*>(out), ldo, o_off, o_head_stride, T, N, K));
+        return ATX_OK;
+    }
     if (x_f32 || dtype == ATX_DT_F32) {
         ATX_HEADOPS_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, head_gemm_kernel<XT, float>,
                                                           reinterpret_cast<const float*>(X), ldx, x_off, x_head_stride,

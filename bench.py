@@ -514,12 +514,13 @@ def routed_trace_measure(world: int, device_ecfg, model: str = "random:8b:0") ->
 
 
 # ------------------------------------------------------------------------------------------------------
-def safisun_measure(args, local, pk) -> dict:
-    """`--workload safisun`: prefill and decode throughput of the Safisun family (state-space, linear-attention and
-    block-local attention mixers) at shapes with the width, depth, feed-forward size and vocabulary of Llama shapes,
-    each beside that Llama shape through the same engine: B prompts of P random tokens (chunked prefill, 8192-token
-    budget) + O greedy tokens, random-init weights, prefix cache off. Steps are timed on the device with CUDA events
-    (the runner's step_events); weights (>= 2.5 GB) exceed L2, so every step streams them from HBM."""
+def safisun_measure(args, local, pk, family: str = "safisun") -> dict:
+    """`--workload safisun | gopopel`: prefill and decode throughput of a layer-list family (Safisun: state-space,
+    linear-attention and block-local attention mixers; Gopopel: parallel layers of latent attention and windowed
+    attention) at shapes with the width, depth, feed-forward size and vocabulary of Llama shapes, each beside that Llama
+    shape (Gopopel also beside the Safisun shape) through the same engine: B prompts of P random tokens (chunked prefill,
+    8192-token budget) + O greedy tokens, random-init weights, prefix cache off. Steps are timed on the device with CUDA
+    events (the runner's step_events); weights (>= 2.5 GB) exceed L2, so every step streams them from HBM."""
     import gc
 
     import numpy as np
@@ -532,7 +533,8 @@ def safisun_measure(args, local, pk) -> dict:
     B, P, O = args.arch_batch, args.arch_prompt, args.arch_out
     records, launches = [], 0
     for size in [x for x in args.arch_sizes.split(",") if x]:
-        for model in (f"random:safisun-{size}:0", f"random:{size}:0"):
+        beside = (f"random:safisun-{size}:0",) if family != "safisun" else ()
+        for model in (f"random:{family}-{size}:0",) + beside + (f"random:{size}:0",):
             src = resolve_model(model)
             ecfg = EngineConfig(max_model_len=P + O + 16, max_num_seqs=B, max_num_batched_tokens=8192,
                                 gpu_memory_utilization=0.5, enable_prefix_caching=False, device=local)
@@ -562,7 +564,10 @@ def safisun_measure(args, local, pk) -> dict:
             pf_ms, pf_tok = sum(x[0] for x in pf), sum(x[1] for x in pf)
             wbytes = mcfg.weight_bytes_per_decode_step()
             state = getattr(mcfg, "state_bytes_per_sequence", lambda: 0)()
-            byts = wbytes + 2 * state * B + mcfg.kv_bytes_per_token() * B * (P + O // 2) * (0 if state else 1)
+            if hasattr(mcfg, "decode_kv_bytes"):      # windowed attention reads at most its window
+                byts = wbytes + mcfg.decode_kv_bytes(P + O // 2) * B
+            else:
+                byts = wbytes + 2 * state * B + mcfg.kv_bytes_per_token() * B * (P + O // 2) * (0 if state else 1)
             records.append({"model": model, "params_bytes": wbytes, "layers": mcfg.num_hidden_layers,
                             "prefill_tokens_per_s": round(pf_tok / pf_ms * 1e3), "prefill_ms_per_8192_tokens":
                             round(pf_ms / pf_tok * 8192, 2),
@@ -576,8 +581,8 @@ def safisun_measure(args, local, pk) -> dict:
             del engine, r
             gc.collect()
             torch.cuda.empty_cache()
-    mine = [x for x in records if "safisun" in x["model"]]
-    return {"metric": "Safisun decode tokens/s beside Llama at equal width, depth, feed-forward and vocabulary",
+    mine = [x for x in records if family in x["model"]]
+    return {"metric": f"{family.capitalize()} decode tokens/s beside Llama at equal width, depth, feed-forward and vocabulary",
             "value": mine[-1]["decode_tokens_per_s"], "ms_per_step": mine[-1]["decode_ms_per_step"], "scaling": "weak",
             "records": records, "gpu_launches": launches, "peak": pk,
             "config": {"workload": f"batch {B} x {P}-token random prompts (chunked prefill, 8192-token budget) + {O} "
@@ -697,8 +702,8 @@ def run_other_workload(args, rank, world, local):
                     "config": {"workload": f"BASELINE configs[4]: Llama-3.1-8B long-context, batch {B} x {P}-token prompts "
                                            f"(chunked prefill, 8192-token budget) + {O} greedy tokens over paged KV",
                                "parallelism": "1 GPU", "kv_blocks": r.num_blocks}})
-    elif args.workload == "safisun":
-        out.update(safisun_measure(args, local, pk))
+    elif args.workload in ("safisun", "gopopel"):
+        out.update(safisun_measure(args, local, pk, args.workload))
         if rank == 0:
             print(json.dumps(out), flush=True)
         if dist is not None:
@@ -732,12 +737,12 @@ def main() -> None:
     ap.add_argument("--no-multi", action="store_true", help="N > 1: skip the routed-DP and 70B-TP records")
     ap.add_argument("--tp70b-any-n", action="store_true", help="attach the 70B tensor-parallel record at any N > 1 "
                                                                "(default: only at N = 8, BASELINE configs[3])")
-    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun: shapes to run (each beside the Llama shape "
+    ap.add_argument("--arch-sizes", default="1b,8b", help="--workload safisun | gopopel: shapes to run (each beside the Llama shape "
                                                           "of the same width, depth, feed-forward and vocabulary)")
     ap.add_argument("--arch-batch", type=int, default=8)
     ap.add_argument("--arch-prompt", type=int, default=2048)
     ap.add_argument("--arch-out", type=int, default=64)
-    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun"],
+    ap.add_argument("--workload", default="fanout", choices=["fanout", "trace", "long", "tp70b", "safisun", "gopopel"],
                     help="fanout = headline BASELINE configs[1] (default); the others are configs[2..4]")
     ap.add_argument("--trace-out", default="", help="directory for response.json / llm_calls.jsonl of a trace replay")
     ap.add_argument("--long-out", type=int, default=128)

@@ -348,7 +348,9 @@ int atx_head_prepare(const float* src, long long ld, const atx_head_seg* segs, i
                      const int* slots, int T, int block_size, float eps, int dtype, int flags, atx_stream_t stream);
 /* A small matrix product per head: out[t, o_off + h * o_head_stride + n] = sum_k X[t, x_off + h * x_head_stride + k] *
  * W[(h * N + n) * ldw + k], times sigmoid(gate[t, h * N + n]) if gate. X fp32 (x_f32 != 0) or of the element type, gate
- * fp32, W and out of the element type. */
+ * fp32, W and out of the element type. bf16 runs on the tensor cores (X rounded to bf16, fp32 accumulation) unless
+ * ATX_FLAG_HEAD_GEMM_FMA asks for the FMA pipe (X as given, bf16 weights widened exactly); fp32 always takes the FMA pipe. */
+#define ATX_FLAG_HEAD_GEMM_FMA 8
 int atx_head_gemm(const void* X, int x_f32, long long ldx, int x_off, int x_head_stride, const void* W, long long ldw,
                   const float* gate, long long ldg, void* out, long long ldo, int o_off, int o_head_stride, int T,
                   int heads, int N, int K, int dtype, int flags, atx_stream_t stream);
@@ -374,6 +376,18 @@ int atx_attn_window_prefill(const void* q, const void* k_cache, const void* v_ca
                             long long ldo, int H, int G, int D, int Vd, int block_size, float scale, float softcap,
                             int chunk, int window, const float* slopes, const float* sinks, int sink, float out_scale,
                             int dtype, int flags, atx_stream_t stream);
+/* atx_attn_window for single decoded tokens on the tensor cores: one CTA per (token, key/value head, slice of the keys),
+ * the query heads that share the key/value head being the rows of its tile (at most 64 of them), so keys and values are
+ * read once per group; `splits` slices leave partial results in `workspace` (..._workspace_bytes(), 8-byte aligned;
+ * none for one slice) and a second kernel folds them. Same shapes as atx_attn_window_prefill. */
+int atx_attn_window_decode_supported(int H, int G, int D, int Vd, long long k_row, long long v_row, int dtype);
+long long atx_attn_window_decode_workspace_bytes(int T, int H, int Vd, int splits);
+int atx_attn_window_decode(const void* q, const void* k_cache, const void* v_cache, long long k_row, long long v_row,
+                           const int* block_tables, int max_blocks, const int* tok_seq, const int* positions,
+                           const float* gate, long long ldg, void* out, long long ldo, void* workspace,
+                           long long workspace_bytes, int splits, int T, int H, int G, int D, int Vd, int block_size,
+                           float scale, float softcap, int chunk, int window, const float* slopes, const float* sinks,
+                           int sink, float out_scale, int dtype, int flags, atx_stream_t stream);
 
 #ifdef __cplusplus
 }

@@ -561,6 +561,28 @@ def test_tensor_core_attention_window_edges_sink_and_slopes(D, Vd, window, pos0,
     torch.cuda.synchronize()
     got2 = o2.float().cpu().double().view(len(rows), H, Vd)
     assert float(((got2 - ref).abs() / scale).max()) < 1e-2
+    # the decode form (heads of a key/value group as the rows of a tile) on single tokens at and around the edges,
+    # the keys in one slice and in several (more slices than some rows have tiles)
+    pick = sorted({0, 1, min(63, total - 1), min(64, total - 1), total // 2, total - 2, total - 1} |
+                  {p for p in (window - 1, window, window + 1, 2 * window) if 0 <= p < total})
+    qd1 = q[pick].to(torch.bfloat16).reshape(len(pick), H * D).contiguous().to(DEV)
+    seq1, pos1 = _i32([0] * len(pick)), _i32(pick)
+    assert lib.atx_attn_window_decode_supported(H, G, D, Vd, k_row, v_row, cabi.DT_BF16) == 1
+    for splits in (1, 3, 7):
+        o3 = torch.zeros(len(pick), H * Vd + 8, device=DEV, dtype=torch.bfloat16)
+        ws = torch.full((max(2, lib.atx_attn_window_decode_workspace_bytes(len(pick), H, Vd, splits) // 4),), float("nan"),
+                        device=DEV)
+        rc = lib.atx_attn_window_decode(qd1.data_ptr(), kc.data_ptr(), vc.data_ptr(), k_row, v_row, bt.data_ptr(), width,
+                                        seq1.data_ptr(), pos1.data_ptr(), None, 0, o3.data_ptr(), H * Vd + 8, ws.data_ptr(),
+                                        ws.numel() * 4, splits, len(pick), H, G, D, Vd, bs, 0.3, 0.0, 0, window,
+                                        sl.data_ptr(), sk.data_ptr(), 1, 1.0, cabi.DT_BF16, 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        torch.cuda.synchronize()
+        got3 = o3[:, :H * Vd].float().cpu().double().view(len(pick), H, Vd)
+        ref3 = want[pick]
+        sc3 = ref3.abs().amax(dim=(1, 2), keepdim=True).clamp(min=1.0)
+        assert float(((got3 - ref3).abs() / sc3).max()) < 2e-2, splits
+        assert float(o3[:, H * Vd:].float().abs().max()) == 0.0
 
 
 def test_a_far_key_among_hundreds_is_found_inside_the_window_and_lost_outside():
@@ -724,3 +746,36 @@ def test_gemm_with_the_squared_relu_in_its_epilogue(T, N, K):
     want = R.relu_squared(x[:T].cpu().double() @ w.cpu().double().T)
     assert torch.allclose(out[:, :N].cpu().double(), want, atol=2e-2, rtol=1e-2)
     assert float((out[:, N:].float() - 3.0).abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("H,G", [(40, 1), (64, 2), (6, 3)])
+def test_decode_attention_with_many_heads_on_one_shared_key_value_row(H, G):
+    """Latent attention's decode shape: many query heads over one cached row per token whose leading part is the value.
+    Tokens of two sequences at different lengths, padded rows between them, slices that some tokens leave empty."""
+    lib, cabi = _lib()
+    D, Vd, bs, window, n = 72, 40, 16, 150, 333
+    g = torch.Generator().manual_seed(H)
+    bf = lambda t: t.to(torch.bfloat16).to(F64)
+    q = bf(torch.randn(n, H, D, generator=g, dtype=F64))
+    k = bf(0.3 * torch.randn(n, G, D, generator=g, dtype=F64))
+    want = R.softmax_attention(q, k, k[:, :, :Vd].contiguous(), 0.2, R.window_mask(n, window))
+    table = torch.randperm(30, generator=g)[:(n + bs - 1) // bs].tolist()
+    pg = _pages(k, table, bs, D, torch.bfloat16)
+    bt = _i32([table + [0] * (32 - len(table)), table + [0] * (32 - len(table))])
+    pick = [n - 1, 0, 5, 149, 150, 151, 200]
+    qd = torch.zeros(len(pick) + 2, H * D, dtype=torch.bfloat16, device=DEV)
+    qd[:len(pick)] = q[pick].to(torch.bfloat16).reshape(len(pick), H * D).to(DEV)
+    seq = _i32([0, 1, 1, 0, 1, 0, 1, -1, -1])                  # two padded rows at the end
+    pos = _i32(pick + [0, 0])
+    for splits in (1, 4, 16):
+        out = torch.full((len(pick) + 2, H * Vd), 9.0, device=DEV, dtype=torch.bfloat16)
+        ws = torch.zeros(max(2, lib.atx_attn_window_decode_workspace_bytes(len(pick) + 2, H, Vd, splits) // 4), device=DEV)
+        rc = lib.atx_attn_window_decode(qd.data_ptr(), pg.data_ptr(), pg.data_ptr(), D, D, bt.data_ptr(), 32, seq.data_ptr(),
+                                        pos.data_ptr(), None, 0, out.data_ptr(), H * Vd, ws.data_ptr(), ws.numel() * 4, splits,
+                                        len(pick) + 2, H, G, D, Vd, bs, 0.2, 0.0, 0, window, None, None, 0, 1.0,
+                                        cabi.DT_BF16, 0, _st())
+        assert rc == 0, lib.atx_last_error()
+        torch.cuda.synchronize()
+        got = out[:len(pick)].float().cpu().double().view(len(pick), H, Vd)
+        assert float((got - want[pick]).abs().max()) < 2e-2, splits
+        assert float((out[len(pick):].float() - 9.0).abs().max()) == 0.0      # padded rows are left alone
