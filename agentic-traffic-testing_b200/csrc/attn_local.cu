@@ -568,28 +568,32 @@ __global__ void __launch_bounds__(128)
 attn_split_merge_kernel(const float* __restrict__ ws, int splits, int vd_pad, int vd_real, const int* __restrict__ tok_seq,
                         const float* __restrict__ gate, long long ldg, __nv_bfloat16* __restrict__ out, long long ldo, int H,
                         float out_scale) {
+    __shared__ float wgt[64];   // weight of every slice: 2^(m_s - M) / sum (at most 64 slices)
     pdl_launch_dependents();
     pdl_wait();
     const long long t = blockIdx.x;
     const int h = blockIdx.y;
     if (tok_seq[t] < 0) return;
     const float* w = ws + (t * H + h) * splits * (vd_pad + 2);
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, w[s * (vd_pad + 2) + vd_pad]);
-    float den = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const float ms = w[s * (vd_pad + 2) + vd_pad];
-        if (ms != -INFINITY) den += w[s * (vd_pad + 2) + vd_pad + 1] * ex2_approx(ms - M);
+    if (threadIdx.x < 32) {   // one warp: every lane fetches the maximum and sum of up to two slices at once
+        const int lane = threadIdx.x;
+        float m0 = -INFINITY, l0 = 0.f, m1 = -INFINITY, l1 = 0.f;
+        if (lane < splits) m0 = w[lane * (vd_pad + 2) + vd_pad], l0 = w[lane * (vd_pad + 2) + vd_pad + 1];
+        if (lane + 32 < splits) m1 = w[(lane + 32) * (vd_pad + 2) + vd_pad], l1 = w[(lane + 32) * (vd_pad + 2) + vd_pad + 1];
+        const float M = warp_max(fmaxf(m0, m1));
+        const float e0 = m0 == -INFINITY ? 0.f : ex2_approx(m0 - M), e1 = m1 == -INFINITY ? 0.f : ex2_approx(m1 - M);
+        const float den = warp_sum(l0 * e0 + l1 * e1);
+        float mul = out_scale / den;
+        if (gate) mul *= 1.f / (1.f + __expf(-gate[t * ldg + h]));
+        wgt[lane] = e0 * mul;
+        wgt[lane + 32] = e1 * mul;
     }
-    float mul = out_scale / den;
-    if (gate) mul *= 1.f / (1.f + __expf(-gate[t * ldg + h]));
+    __syncthreads();
     for (int d = threadIdx.x; d < vd_real; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = w[s * (vd_pad + 2) + vd_pad];
-            if (ms != -INFINITY) acc = fmaf(w[s * (vd_pad + 2) + d], ex2_approx(ms - M), acc);
-        }
-        out[t * ldo + static_cast<long long>(h) * vd_real + d] = __float2bfloat16_rn(acc * mul);
+#pragma unroll 4
+        for (int s = 0; s < splits; ++s) acc = fmaf(w[s * (vd_pad + 2) + d], wgt[s], acc);
+        out[t * ldo + static_cast<long long>(h) * vd_real + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -842,7 +846,7 @@ int atx_attn_window_decode(const void* q, const void* k_cache, const void* v_cac
                            int sink, float out_scale, int dtype, int flags, atx_stream_t stream) {
     ATX_REQUIRE(q && k_cache && v_cache && block_tables && tok_seq && positions && out, "atx_attn_window_decode: null pointer");
     ATX_REQUIRE(T > 0 && H > 0 && G > 0 && H % G == 0 && block_size > 0 && chunk >= 0 && window >= 0 && k_row >= D &&
-                    v_row >= Vd && ldo % 2 == 0 && splits >= 1 && splits <= 65535 && G <= 65535,
+                    v_row >= Vd && ldo % 2 == 0 && splits >= 1 && splits <= 64 && G <= 65535,
                 "atx_attn_window_decode: bad shape T=%d H=%d G=%d k_row=%lld v_row=%lld ldo=%lld splits=%d", T, H, G, k_row,
                 v_row, ldo, splits);
     if (!atx_attn_window_decode_supported(H, G, D, Vd, k_row, v_row, dtype) ||

@@ -152,12 +152,6 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
     const float* x = src + t * ld + s.src_off + static_cast<long long>(hh) * s.src_stride;
     const XT* nw = reinterpret_cast<const XT*>(s.norm_w);
     float r = 1.f;
-    if (s.norm_dims > 0) {
-        float ss = 0.f;
-        for (int i = lane; i < s.norm_dims; i += 32) ss = fmaf(x[i], x[i], ss);
-        ss = warp_sum(ss);
-        r = rsqrtf(ss / static_cast<float>(s.norm_dims) + eps);
-    }
     const float* cs = nullptr;
     const int half = s.rot_dims / 2;
     if (s.rot_dims > 0) cs = s.rot + static_cast<long long>(positions[t]) * s.rot_dims;
@@ -170,6 +164,61 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
         dst = reinterpret_cast<XT*>(s.dst) + t * s.dst_ld + s.dst_off + static_cast<long long>(hh) * s.dst_stride;
     }
     const long long flat = (t * s.heads + hh) * s.width;   // index into mix_src / save
+    // Four elements per access where every offset, pitch and count of the slice is a multiple of four and the pointers
+    // are aligned: a rotated pair then lies inside one access, so no partner has to be fetched.
+    const bool vec =
+        ((s.width | s.src_off | s.src_stride | s.norm_dims | s.rot_off | s.dst_off | s.dst_stride) & 3) == 0 && (ld & 3) == 0 &&
+        (s.dst_kind == ATX_HEAD_DST_PAGES || (s.dst_ld & 3) == 0) &&
+        ((reinterpret_cast<unsigned long long>(src) | reinterpret_cast<unsigned long long>(s.dst) |
+          reinterpret_cast<unsigned long long>(s.norm_w) | reinterpret_cast<unsigned long long>(s.mix_src) |
+          reinterpret_cast<unsigned long long>(s.save)) & 15) == 0;
+    if (vec) {
+        if (s.norm_dims > 0) {
+            float ss = 0.f;
+#pragma unroll 4
+            for (int i4 = lane; i4 < s.norm_dims / 4; i4 += 32) {
+                const float4 v = hld4(x, i4);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+            ss = warp_sum(ss);
+            r = rsqrtf(ss / static_cast<float>(s.norm_dims) + eps);
+        }
+#pragma unroll 2
+        for (int i4 = lane; i4 < s.width / 4; i4 += 32) {
+            const float4 v = hld4(x, i4);
+            float e[4] = {v.x, v.y, v.z, v.w};
+            const int i = 4 * i4;
+            if (i < s.norm_dims) {
+                const float4 g = hld4(nw, i4);
+                e[0] *= r * g.x, e[1] *= r * g.y, e[2] *= r * g.z, e[3] *= r * g.w;
+            }
+#pragma unroll
+            for (int p2 = 0; p2 < 2; ++p2) {
+                const int j = i + 2 * p2 - s.rot_off;
+                if (j >= 0 && j < s.rot_dims) {
+                    const float c = cs[j >> 1], sn = cs[half + (j >> 1)];
+                    const float a0 = e[2 * p2], b0 = e[2 * p2 + 1];
+                    e[2 * p2] = fmaf(a0, c, -(b0 * sn));
+                    e[2 * p2 + 1] = fmaf(b0, c, a0 * sn);
+                }
+            }
+            if (s.save) *reinterpret_cast<float4*>(s.save + flat + i) = make_float4(e[0], e[1], e[2], e[3]);
+            if (s.mix_src) {
+                const float4 mv = *reinterpret_cast<const float4*>(s.mix_src + flat + i);
+                e[0] = fmaf(s.mix, mv.x - e[0], e[0]), e[1] = fmaf(s.mix, mv.y - e[1], e[1]);
+                e[2] = fmaf(s.mix, mv.z - e[2], e[2]), e[3] = fmaf(s.mix, mv.w - e[3], e[3]);
+            }
+            hst4(dst, i4, make_float4(e[0], e[1], e[2], e[3]));
+        }
+        return;
+    }
+    if (s.norm_dims > 0) {
+        float ss = 0.f;
+#pragma unroll 4
+        for (int i = lane; i < s.norm_dims; i += 32) ss = fmaf(x[i], x[i], ss);
+        ss = warp_sum(ss);
+        r = rsqrtf(ss / static_cast<float>(s.norm_dims) + eps);
+    }
     auto normed = [&](int i) -> float {
         float v = x[i];
         if (i < s.norm_dims) v = v * r * hld(nw, i);
@@ -272,13 +321,36 @@ head_gemm_tc_kernel(const XI* __restrict__ X, long long ldx, int x_off, int xs, 
     float acc[kHT / 8][4];
 #pragma unroll
     for (int i = 0; i < kHT / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+    // eight elements per access where pitches, offsets and K allow it (rows past T or N and columns past K stay zero)
+    const bool vec = ((K | x_off | xs) & 7) == 0 && ((ldx | ldw) & 7) == 0 &&
+                     ((reinterpret_cast<unsigned long long>(X) | reinterpret_cast<unsigned long long>(W)) & 15) == 0;
     for (int k0 = 0; k0 < K; k0 += kHKC) {
-        for (int e = threadIdx.x; e < kHT * kHKC; e += 128) {
-            const int r = e / kHKC, kk = e - r * kHKC;
-            const int t = t0 + r, n = n0 + r, k = k0 + kk;
-            const float xv = (t < T && k < K) ? hld(Xh, static_cast<long long>(t) * ldx + k) : 0.f;
-            sx[r * kHLD + kk] = __float2bfloat16_rn(xv);
-            sw[r * kHLD + kk] = (n < N && k < K) ? Wh[static_cast<long long>(n) * ldw + k] : __float2bfloat16_rn(0.f);
+        if (vec) {
+            for (int e = threadIdx.x; e < kHT * (kHKC / 8); e += 128) {
+                const int r = e / (kHKC / 8), k8 = (e - r * (kHKC / 8)) * 8;
+                const int t = t0 + r, n = n0 + r, k = k0 + k8;
+                uint4 xv = make_uint4(0, 0, 0, 0), wv = make_uint4(0, 0, 0, 0);
+                if (t < T && k < K) {
+                    if constexpr (sizeof(XI) == 4) {
+                        const float4 a = *reinterpret_cast<const float4*>(Xh + static_cast<long long>(t) * ldx + k);
+                        const float4 b = *reinterpret_cast<const float4*>(Xh + static_cast<long long>(t) * ldx + k + 4);
+                        xv = make_uint4(pack_bf16(a.x, a.y), pack_bf16(a.z, a.w), pack_bf16(b.x, b.y), pack_bf16(b.z, b.w));
+                    } else {
+                        xv = *reinterpret_cast<const uint4*>(Xh + static_cast<long long>(t) * ldx + k);
+                    }
+                }
+                if (n < N && k < K) wv = __ldg(reinterpret_cast<const uint4*>(Wh + static_cast<long long>(n) * ldw + k));
+                *reinterpret_cast<uint4*>(sx + r * kHLD + k8) = xv;
+                *reinterpret_cast<uint4*>(sw + r * kHLD + k8) = wv;
+            }
+        } else {
+            for (int e = threadIdx.x; e < kHT * kHKC; e += 128) {
+                const int r = e / kHKC, kk = e - r * kHKC;
+                const int t = t0 + r, n = n0 + r, k = k0 + kk;
+                const float xv = (t < T && k < K) ? hld(Xh, static_cast<long long>(t) * ldx + k) : 0.f;
+                sx[r * kHLD + kk] = __float2bfloat16_rn(xv);
+                sw[r * kHLD + kk] = (n < N && k < K) ? Wh[static_cast<long long>(n) * ldw + k] : __float2bfloat16_rn(0.f);
+            }
         }
         __syncthreads();
 #pragma unroll

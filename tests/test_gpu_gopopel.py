@@ -617,12 +617,14 @@ def test_a_far_key_among_hundreds_is_found_inside_the_window_and_lost_outside():
         assert (float(out[0, 3]) > 0.99) == seen
 
 
-def test_head_preparation_norms_rotates_blends_and_writes_pages():
+@pytest.mark.parametrize("D,Vd,pad,qo_off,lp_off", [(10, 6, 3, 1, 2), (12, 8, 4, 4, 4)])
+def test_head_preparation_norms_rotates_blends_and_writes_pages(D, Vd, pad, qo_off, lp_off):
+    """Sizes and offsets off the four-element path, and on it."""
     lib, cabi = _lib()
     T, bs = 37, 16
     g = torch.Generator().manual_seed(2)
-    H, D, G, Vd, C, Rr, rd = 3, 10, 2, 6, 12, 8, 4
-    ld = H * D + G * Vd + C + Rr + 3
+    H, G, C, Rr, rd = 3, 2, 12, 8, 4
+    ld = H * D + G * Vd + C + Rr + pad
     src = torch.randn(T, ld, generator=g, dtype=F64)
     qw, cw = 1 + 0.1 * torch.randn(D, generator=g, dtype=F64), 1 + 0.1 * torch.randn(C, generator=g, dtype=F64)
     first = torch.randn(T, G, Vd, generator=g, dtype=F64)
@@ -631,27 +633,27 @@ def test_head_preparation_norms_rotates_blends_and_writes_pages():
     from atx.models.common import rotation_table
     table = rotation_table(50.0, rd, 200, torch.device(DEV))
     srcd = src.float().to(DEV).contiguous()
-    qo = torch.full((T, H * D + 2), 7.0, device=DEV)
+    qo = torch.full((T, H * D + 2 * qo_off), 7.0, device=DEV)
     vpg = torch.full(((T + 11 + bs - 1) // bs, G, bs, Vd), float("nan"), device=DEV)
-    lpg = torch.full(((T + 11 + bs - 1) // bs, 1, bs, C + Rr + 4), float("nan"), device=DEV)
+    lpg = torch.full(((T + 11 + bs - 1) // bs, 1, bs, C + Rr + 2 * lp_off), float("nan"), device=DEV)
     saved = torch.zeros(T, G * Vd, device=DEV)
     qwd, cwd, fd = qw.float().to(DEV), cw.float().to(DEV), first.float().reshape(T, G * Vd).contiguous().to(DEV)
     S = cabi.HeadSeg
     sg = cabi.head_segs(
         S(src_off=0, src_stride=D, heads=H, width=D, norm_dims=D, norm_w=qwd.data_ptr(), dst_kind=cabi.HEAD_DST_ROWS,
-          dst=qo.data_ptr(), dst_ld=H * D + 2, dst_off=1, dst_stride=D),
+          dst=qo.data_ptr(), dst_ld=H * D + 2 * qo_off, dst_off=qo_off, dst_stride=D),
         S(src_off=H * D, src_stride=Vd, heads=G, width=Vd, mix=0.3, mix_src=fd.data_ptr(), save=saved.data_ptr(),
           dst_kind=cabi.HEAD_DST_PAGES, dst=vpg.data_ptr(), dst_off=0, dst_stride=Vd),
         S(src_off=H * D + G * Vd, src_stride=C + Rr, heads=1, width=C + Rr, norm_dims=C, norm_w=cwd.data_ptr(), rot_off=C,
-          rot_dims=rd, rot=table.data_ptr(), dst_kind=cabi.HEAD_DST_PAGES, dst=lpg.data_ptr(), dst_off=2,
-          dst_stride=C + Rr + 4))
+          rot_dims=rd, rot=table.data_ptr(), dst_kind=cabi.HEAD_DST_PAGES, dst=lpg.data_ptr(), dst_off=lp_off,
+          dst_stride=C + Rr + 2 * lp_off))
     posd, slotd = _i32(pos), _i32(perm)
     rc = lib.atx_head_prepare(srcd.data_ptr(), ld, sg, 3, posd.data_ptr(), slotd.data_ptr(), T, bs, 1e-4, cabi.DT_F32, 0, _st())
     assert rc == 0, lib.atx_last_error()
     torch.cuda.synchronize()
     wq = R.unit_rms(src[:, :H * D].view(T, H, D), qw, 1e-4)
-    assert torch.allclose(qo[:, 1:1 + H * D].cpu().double().view(T, H, D), wq, atol=1e-5)
-    assert float(qo[:, 0].min()) == 7.0 and float(qo[:, -1].min()) == 7.0
+    assert torch.allclose(qo[:, qo_off:qo_off + H * D].cpu().double().view(T, H, D), wq, atol=1e-5)
+    assert float(qo[:, :qo_off].min()) == 7.0 and float(qo[:, qo_off + H * D:].min()) == 7.0
     vraw = src[:, H * D:H * D + G * Vd].view(T, G, Vd)
     assert torch.allclose(saved.cpu().double().view(T, G, Vd), vraw, atol=1e-6)
     lat = src[:, H * D + G * Vd:H * D + G * Vd + C + Rr]
@@ -660,8 +662,8 @@ def test_head_preparation_norms_rotates_blends_and_writes_pages():
     for t in range(T):
         b, o = perm[t] // bs, perm[t] % bs
         assert torch.allclose(vpg[b, :, o].cpu().double(), 0.7 * vraw[t] + 0.3 * first[t], atol=1e-5)
-        assert torch.allclose(lpg[b, 0, o, 2:2 + C + Rr].cpu().double(), wl[t], atol=1e-5)
-        assert torch.isnan(lpg[b, 0, o, :2]).all() and torch.isnan(lpg[b, 0, o, 2 + C + Rr:]).all()
+        assert torch.allclose(lpg[b, 0, o, lp_off:lp_off + C + Rr].cpu().double(), wl[t], atol=1e-5)
+        assert torch.isnan(lpg[b, 0, o, :lp_off]).all() and torch.isnan(lpg[b, 0, o, lp_off + C + Rr:]).all()
     assert int(torch.isfinite(vpg[:, 0, :, 0]).sum()) == T                  # nothing was written anywhere else
 
 
@@ -699,26 +701,27 @@ def test_tanh_norm_activation_head_gemm_and_scaled_embedding_match_their_formula
         z = x.float().double()
         gelu = 0.5 * z * (1 + torch.tanh((2 / torch.pi) ** 0.5 * (z + 0.044715 * z ** 3)))
         assert torch.allclose(act[:, :W].cpu().double(), gelu, atol=tol, rtol=tol)
-    # per-head products, fp32 rows in and rows of the element type in, with and without the gate
-    T, H, N, K = 70, 3, 20, 13
-    X = rt(torch.randn(T, H * (K + 2) + 1, generator=g, dtype=F64))
-    Wm = rt(torch.randn(H * N, K + 3, generator=g, dtype=F64) / K ** 0.5)
-    gate = torch.randn(T, H * N + 5, generator=g, dtype=F64)
-    ref = torch.einsum("thk,hnk->thn", torch.stack([X[:, 1 + h * (K + 2):1 + h * (K + 2) + K] for h in range(H)], 1),
-                       Wm[:, :K].view(H, N, K))
-    gd, Wd = gate.float().to(DEV), Wm.to(xt).to(DEV)
-    for x_f32 in (1, 0):
-        Xd = X.float().to(DEV) if x_f32 else X.to(xt).to(DEV)
-        for gated in (False, True):
-            out = torch.zeros(T, 2 + H * (N + 1), dtype=xt, device=DEV)
-            rc = lib.atx_head_gemm(Xd.data_ptr(), x_f32, X.shape[1], 1, K + 2, Wd.data_ptr(), K + 3,
-                                   gd.data_ptr() if gated else None, H * N + 5, out.data_ptr(), out.shape[1], 2, N + 1, T, H, N,
-                                   K, dt, 0, _st())
-            assert rc == 0, lib.atx_last_error()
-            torch.cuda.synchronize()
-            want = ref * torch.sigmoid(gate.float().double()[:, :H * N].view(T, H, N)) if gated else ref
-            got = torch.stack([out[:, 2 + h * (N + 1):2 + h * (N + 1) + N] for h in range(H)], 1).cpu().double()
-            assert torch.allclose(got, want, atol=10 * tol, rtol=tol), (x_f32, gated)
+    # per-head products, fp32 rows in and rows of the element type in, with and without the gate; sizes off and on the
+    # eight-element staging path of the tensor-core kernel, a reduction longer than one staged chunk
+    for T, H, N, K, xo, xp, wp in ((70, 3, 20, 13, 1, 2, 3), (150, 2, 72, 136, 8, 8, 8)):
+        X = rt(torch.randn(T, H * (K + xp) + xo, generator=g, dtype=F64))
+        Wm = rt(torch.randn(H * N, K + wp, generator=g, dtype=F64) / K ** 0.5)
+        gate = torch.randn(T, H * N + 5, generator=g, dtype=F64)
+        ref = torch.einsum("thk,hnk->thn", torch.stack([X[:, xo + h * (K + xp):xo + h * (K + xp) + K] for h in range(H)], 1),
+                           Wm[:, :K].view(H, N, K))
+        gd, Wd = gate.float().to(DEV), Wm.to(xt).to(DEV)
+        for x_f32 in (1, 0):
+            Xd = X.float().to(DEV) if x_f32 else X.to(xt).to(DEV)
+            for gated, fl in ((False, 0), (True, 0), (True, cabi.FLAG_HEAD_GEMM_FMA)):
+                out = torch.zeros(T, 2 + H * (N + 1), dtype=xt, device=DEV)
+                rc = lib.atx_head_gemm(Xd.data_ptr(), x_f32, X.shape[1], xo, K + xp, Wd.data_ptr(), K + wp,
+                                       gd.data_ptr() if gated else None, H * N + 5, out.data_ptr(), out.shape[1], 2, N + 1, T,
+                                       H, N, K, dt, fl, _st())
+                assert rc == 0, lib.atx_last_error()
+                torch.cuda.synchronize()
+                want = ref * torch.sigmoid(gate.float().double()[:, :H * N].view(T, H, N)) if gated else ref
+                got = torch.stack([out[:, 2 + h * (N + 1):2 + h * (N + 1) + N] for h in range(H)], 1).cpu().double()
+                assert torch.allclose(got, want, atol=10 * tol, rtol=tol), (x_f32, gated, fl)
     # embedding rows times a scale
     V, W = 50, 24
     tab = rt(torch.randn(V, W, generator=g, dtype=F64))
