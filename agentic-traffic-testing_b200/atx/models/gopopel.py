@@ -428,7 +428,7 @@ class Program:
                     self.rot[key] = rotation_table(key[0], key[1], e.max_model_len, dev)
         self.first_mix = cfg.first_mix_layer()
         # scratch of the decode attention's key slices: [tokens, heads, slices, value width + 2] fp32
-        self.max_splits = 16
+        self.max_splits = 32
         self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
         h_max = max(spec["mixer"]["heads"] for spec in cfg.layers)
         self.split_ws = torch.zeros(max(2, r.Smax * h_max * self.max_splits * (128 + 2)), dtype=f32, device=dev)
@@ -446,10 +446,10 @@ class Program:
         n = 0
         if rows and rows == n_dec and lib.atx_attn_window_decode_supported(H, G, D, Vd, k_row, v_row, dt):
             # decoded tokens: the heads of a key/value group as the rows of a tensor-core tile, the keys cut into slices
-            # (as many as fill the GPU about twice, by the longest span a query of this layer can see: a fixed number per
+            # (as many as fill the GPU about three times, by the longest span a query of this layer can see: a fixed number per
             # layer and batch size, so a captured graph stays valid)
             keys = min(window or r.e.max_model_len, r.e.max_model_len)
-            splits = max(1, min((keys + 63) // 64, self.max_splits, -(-2 * self.sms // (rows * G))))
+            splits = max(1, min((keys + 63) // 64, self.max_splits, -(-3 * self.sms // (rows * G))))
             ws = self.split_ws
             ck(lib.atx_attn_window_decode(q, kc, vc, k_row, v_row, dp["seq_bt"], r.MB, dp["tok_seq"], dp["pos"], None, 0, out,
                                           ldo, ws.data_ptr(), ws.numel() * 4, splits, rows, H, G, D, Vd, r.bs, scale, 0.0, 0,

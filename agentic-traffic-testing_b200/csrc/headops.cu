@@ -129,15 +129,31 @@ struct PrepArgs {
     atx_head_seg seg[ATX_HEAD_SEGS_MAX];
 };
 
-// One warp per (row, head). A lane owns single elements; a rotated element also reads its partner of the pair.
-template <typename XT>
+// One warp per (row, head); WIDE: one CTA per (row, head), for steps of few rows whose heads are wide (a bottleneck of
+// a thousand elements normed by one warp is a chain of dependent loads). A lane owns single elements (or four); a rotated
+// element also reads its partner of the pair.
+template <typename XT, bool WIDE>
 __global__ void __launch_bounds__(256)
 head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __restrict__ positions,
                     const int* __restrict__ slots, int T, int bs, float eps, const __grid_constant__ PrepArgs a) {
+    __shared__ float red[8];
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long long wid = static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    constexpr int kStep = WIDE ? 256 : 32;
+    const int lane = WIDE ? threadIdx.x : (threadIdx.x & 31);
+    const long long wid = WIDE ? static_cast<long long>(blockIdx.x)
+                               : static_cast<long long>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    auto head_sum = [&](float v) -> float {   // over the threads that share the head
+        v = warp_sum(v);
+        if constexpr (WIDE) {
+            if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+            __syncthreads();
+            v = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v += red[i];
+        }
+        return v;
+    };
     if (wid >= static_cast<long long>(T) * a.total_heads) return;
     const long long t = wid / a.total_heads;
     int hh = static_cast<int>(wid - t * a.total_heads);
@@ -176,15 +192,15 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
         if (s.norm_dims > 0) {
             float ss = 0.f;
 #pragma unroll 4
-            for (int i4 = lane; i4 < s.norm_dims / 4; i4 += 32) {
+            for (int i4 = lane; i4 < s.norm_dims / 4; i4 += kStep) {
                 const float4 v = hld4(x, i4);
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
-            ss = warp_sum(ss);
+            ss = head_sum(ss);
             r = rsqrtf(ss / static_cast<float>(s.norm_dims) + eps);
         }
 #pragma unroll 2
-        for (int i4 = lane; i4 < s.width / 4; i4 += 32) {
+        for (int i4 = lane; i4 < s.width / 4; i4 += kStep) {
             const float4 v = hld4(x, i4);
             float e[4] = {v.x, v.y, v.z, v.w};
             const int i = 4 * i4;
@@ -215,8 +231,8 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
     if (s.norm_dims > 0) {
         float ss = 0.f;
 #pragma unroll 4
-        for (int i = lane; i < s.norm_dims; i += 32) ss = fmaf(x[i], x[i], ss);
-        ss = warp_sum(ss);
+        for (int i = lane; i < s.norm_dims; i += kStep) ss = fmaf(x[i], x[i], ss);
+        ss = head_sum(ss);
         r = rsqrtf(ss / static_cast<float>(s.norm_dims) + eps);
     }
     auto normed = [&](int i) -> float {
@@ -224,7 +240,7 @@ head_prepare_kernel(const float* __restrict__ src, long long ld, const int* __re
         if (i < s.norm_dims) v = v * r * hld(nw, i);
         return v;
     };
-    for (int i = lane; i < s.width; i += 32) {
+    for (int i = lane; i < s.width; i += kStep) {
         float v = normed(i);
         const int j = i - s.rot_off;
         if (j >= 0 && j < s.rot_dims) {
@@ -456,14 +472,21 @@ int atx_head_prepare(const float* src, long long ld, const atx_head_seg* segs, i
         a.total_heads += s.heads;
     }
     const long long warps = static_cast<long long>(T) * a.total_heads;
+    int widest = 0;
+    for (int i = 0; i < n_segs; ++i) widest = segs[i].width > widest ? segs[i].width : widest;
+    const bool wide = widest >= 512 && warps <= 1024;   // few, wide heads: a CTA each
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
-    cfg.gridDim = dim3(static_cast<unsigned>((warps + 7) / 8));
+    cfg.gridDim = dim3(static_cast<unsigned>(wide ? warps : (warps + 7) / 8));
     cfg.blockDim = dim3(256);
     cfg.stream = reinterpret_cast<cudaStream_t>(stream);
     set_pdl_attr(cfg, attr, flags);
-    ATX_HEADOPS_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, head_prepare_kernel<XT>, src, ld, positions, slots, T,
-                                                      block_size, eps, a)));
+    if (wide)
+        ATX_HEADOPS_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, head_prepare_kernel<XT, true>, src, ld, positions, slots, T,
+                                                          block_size, eps, a)));
+    else
+        ATX_HEADOPS_XT(dtype, ATX_CUDA(cudaLaunchKernelEx(&cfg, head_prepare_kernel<XT, false>, src, ld, positions, slots, T,
+                                                          block_size, eps, a)));
     return ATX_OK;
 }
 

@@ -617,13 +617,14 @@ def test_a_far_key_among_hundreds_is_found_inside_the_window_and_lost_outside():
         assert (float(out[0, 3]) > 0.99) == seen
 
 
-@pytest.mark.parametrize("D,Vd,pad,qo_off,lp_off", [(10, 6, 3, 1, 2), (12, 8, 4, 4, 4)])
-def test_head_preparation_norms_rotates_blends_and_writes_pages(D, Vd, pad, qo_off, lp_off):
-    """Sizes and offsets off the four-element path, and on it."""
+@pytest.mark.parametrize("D,Vd,pad,qo_off,lp_off,C", [(10, 6, 3, 1, 2, 12), (12, 8, 4, 4, 4, 12), (10, 6, 3, 1, 2, 530),
+                                                       (12, 8, 4, 4, 4, 640)])
+def test_head_preparation_norms_rotates_blends_and_writes_pages(D, Vd, pad, qo_off, lp_off, C):
+    """Sizes and offsets off the four-element path and on it; a wide bottleneck takes a CTA per head instead of a warp."""
     lib, cabi = _lib()
     T, bs = 37, 16
     g = torch.Generator().manual_seed(2)
-    H, G, C, Rr, rd = 3, 2, 12, 8, 4
+    H, G, Rr, rd = 3, 2, 8, 4
     ld = H * D + G * Vd + C + Rr + pad
     src = torch.randn(T, ld, generator=g, dtype=F64)
     qw, cw = 1 + 0.1 * torch.randn(D, generator=g, dtype=F64), 1 + 0.1 * torch.randn(C, generator=g, dtype=F64)
