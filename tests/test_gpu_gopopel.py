@@ -55,7 +55,8 @@ def engine(cfg, wt, dtype="float32", **kw):
     w = gopopel.Weights.from_state_dict(mcfg, wt, torch.device(DEV), xt)
     ecfg = EngineConfig(max_model_len=kw.pop("max_model_len", 256), max_num_seqs=kw.pop("max_num_seqs", 4),
                         max_num_batched_tokens=kw.pop("max_num_batched_tokens", 256),
-                        num_gpu_blocks=kw.pop("num_gpu_blocks", 64), enable_prefix_caching=False,
+                        num_gpu_blocks=kw.pop("num_gpu_blocks", 64),
+                        enable_prefix_caching=kw.pop("enable_prefix_caching", False),
                         enable_cuda_graphs=kw.pop("enable_cuda_graphs", False),
                         async_scheduling=kw.pop("async_scheduling", False), dtype=dtype,
                         max_logit_rows=kw.pop("max_logit_rows", 256), **kw)
@@ -314,14 +315,14 @@ def drawn_model(rng):
         kv, vd = vshape if mixing else (rng.choice([1, 2, 4]), rng.choice([16, 40, 64, 128]))
         d = rng.choice([16, 32, 64, 96, 128])
         return {"dim": d, "heads": kv * rng.choice([1, 2, 3, 4]), "kv_heads": kv,
-                "mask": {"size": rng.choice([1, 16, 33, 64, 100, 136, 500])}, "scale": rng.choice([d ** -0.5, 0.05, 0.11]),
+                "mask": {"size": rng.choice([1, 16, 33, 64, 100, 140, 500])}, "scale": rng.choice([d ** -0.5, 0.05, 0.11]),
                 "v_mix": mixing, "vdim": vd}
 
     def latent():
         r = rng.choice([8, 16, 32, 64])
         d = rng.choice([16, 32, 64])
         return {"dim": d, "heads": rng.choice([1, 2, 4, 6]), "kv_rank": rng.choice([24, 64, 96, 128, 200]),
-                "mask": {"size": rng.choice([2, 17, 64, 72, 130, 400])}, "q_rank": rng.choice([32, 64, 96, 192]),
+                "mask": {"size": rng.choice([2, 17, 64, 75, 130, 400])}, "q_rank": rng.choice([32, 64, 96, 192]),
                 "rot": {"base": rng.choice([1e2, 1e4, 5e5]), "dims": rng.choice([x for x in (2, 8, 16, 32, 64) if x <= r])},
                 "rot_dim": r, "scale": rng.choice([(d + r) ** -0.5, 0.08]), "vdim": rng.choice([16, 32, 80, 128])}
 
@@ -407,6 +408,26 @@ def test_greedy_generation_matches_the_reference(mode):
         for i, tok in enumerate(o):            # teacher-forced: every token is the reference's arg-max (ties aside)
             assert tok == int(lg[i].argmax()) or float(top2[i, 0] - top2[i, 1]) < 1e-4, (mode, i)
     assert eng.allocator.num_free == eng.allocator.num_blocks
+    eng.runner.close()
+
+
+def test_generation_over_a_cached_prefix_matches_the_reference():
+    """Pages of a shared prefix are attached from the block cache instead of being computed again: they hold blended
+    values and latent rows, which depend on the token and its position only, so the continuation must not change."""
+    from atx.scheduler import SamplingParams
+
+    cfg = mixed_model()
+    wt = R.random_checkpoint(cfg, 21)
+    common = tokens(50, seed=9)
+    prompts = [common + tokens(7, seed=1), common + tokens(12, seed=2), common[:33] + tokens(3, seed=3)]
+    eng = engine(cfg, wt, enable_prefix_caching=True)
+    outs = [eng.generate_sync([p], SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True))[0] for p in prompts]
+    assert eng.allocator.hits >= 3 + 2                      # 48 and 32 tokens of full pages were found again
+    for p, o in zip(prompts, outs):
+        lg = R.forward(cfg, wt, p + o[:-1])[len(p) - 1:]
+        top2 = lg.topk(2, dim=-1).values
+        for i, tok in enumerate(o):
+            assert tok == int(lg[i].argmax()) or float(top2[i, 0] - top2[i, 1]) < 1e-4, i
     eng.runner.close()
 
 
