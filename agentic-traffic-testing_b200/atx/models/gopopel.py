@@ -41,7 +41,7 @@ from typing import Dict, List, Optional, Tuple
 import torch
 
 from .. import _cabi
-from .common import _Linear, _use_tc, rotation_table
+from .common import _Linear, rotation_table
 
 # ---- configuration --------------------------------------------------------------------------------------------------
 

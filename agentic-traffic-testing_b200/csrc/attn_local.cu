@@ -2,9 +2,13 @@
 // over the whole q (and k) projection, rotation of the first `rot_dims` dimensions of a head in adjacent pairs,
 // a tanh cap on the scores, a block-local causal mask (a query sees the keys of its own block of `chunk` positions),
 // a zero-score sink in the softmax denominator, a sigmoid gate per head on the output, any head sizes (the value size
-// may differ from the query/key size). One kernel serves prompt portions and single decoded tokens: a warp owns one
-// (row, head) and walks the keys of its block 32 at a time; scores, softmax and accumulation are fp32.
-// Cache element type XT = bf16 or fp32. Pages hold `bs` tokens: K [blocks, G, bs, D], V [blocks, G, bs, Vd].
+// may differ from the query/key size); and, each optional: a sliding window, a penalty per head and unit of distance,
+// a learned sink score per head, key and value rows wider than the heads (so that both can share one page array).
+// The row kernel serves prompt portions and single decoded tokens alike: a warp owns one (row, head) and walks the keys
+// it sees 32 at a time; scores, softmax and accumulation are fp32. For bf16 pages there are two tensor-core forms of
+// the same arithmetic further down: 64 consecutive rows of a prompt portion per CTA, and (decoded tokens) the query
+// heads of one key/value group as the rows of a tile, with the keys cut into slices.
+// Cache element type XT = bf16 or fp32. Pages hold `bs` tokens: K [blocks, G, bs, k_row], V [blocks, G, bs, v_row].
 #include "common.cuh"
 
 #include "../../include/atx_b200.h"

@@ -67,9 +67,7 @@ tanh_norm_kernel(const float* __restrict__ x, const int* __restrict__ rows, floa
                  long long zero_vecs) {
     pdl_launch_dependents();
     if (static_cast<int>(blockIdx.x) >= T) {
-        // nothing upstream reads this buffer any more once the producer of x has been launched; still wait, a GEMM of
-        // the previous layer may be adding into it
-        pdl_wait();
+        pdl_wait();   // a kernel of the previous layer may still be reading the buffer
         const long long nb = gridDim.x - T, b0 = blockIdx.x - T;
         for (long long i = b0 * blockDim.x + threadIdx.x; i < zero_vecs; i += nb * blockDim.x)
             zero_ptr[i] = make_uint4(0, 0, 0, 0);
