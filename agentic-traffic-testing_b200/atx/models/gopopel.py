@@ -70,8 +70,10 @@ class Config:
     def validate(self) -> None:
         vshape = None
         for i, l in enumerate(self.layers):
-            c = l["mixer"]
+            c = l["mixer"] = dict(l["mixer"])
             if l["type"] == "attention":
+                c.setdefault("kv_heads", c["heads"])      # keys a configuration may leave out where the meaning is plain
+                c.setdefault("vdim", c["dim"])
                 if c["heads"] % c["kv_heads"]:
                     raise ValueError(f"layer {i}: {c['heads']} heads over {c['kv_heads']} key/value heads")
                 if c.get("v_mix"):
@@ -80,7 +82,11 @@ class Config:
                         raise ValueError(f"layer {i}: value blending needs the value shape {vshape} of the first such layer")
                     vshape = sh
             elif l["type"] == "latent_attention":
-                rd = int((c.get("rot") or {}).get("dims", 0))
+                c["rot"] = dict(c.get("rot") or {})
+                c["rot"].setdefault("dims", c["rot_dim"])  # the rotated part turns as a whole unless told otherwise
+                c["rot"].setdefault("base", 10000.0)
+                c.setdefault("vdim", c["dim"])
+                rd = int(c["rot"]["dims"])
                 if rd % 2 or rd > c["rot_dim"]:
                     raise ValueError(f"layer {i}: rot.dims={rd} must be even and at most rot_dim={c['rot_dim']}")
             else:

@@ -41,6 +41,11 @@ def test_config_is_read_from_json_and_picked_by_architecture(tmp_path):
     assert resolve_model(str(tmp_path)).config.tensor_shapes() == m.tensor_shapes()
     with pytest.raises(ValueError):
         gopopel.Config.from_json(dict(cfg, layers=[{"type": "conv", "mixer": {}, "mlp": None}]))
+    short = json.loads(json.dumps(cfg))                  # keys with a plain default may be left out
+    del short["layers"][0]["mixer"]["rot"]["dims"], short["layers"][2]["mixer"]["kv_heads"]
+    ms = gopopel.Config.from_json(short)
+    assert ms.layers[0]["mixer"]["rot"]["dims"] == 4 and ms.layers[2]["mixer"]["kv_heads"] == 2
+    assert ms.tensor_shapes() == m.tensor_shapes()
     bad = json.loads(json.dumps(cfg))
     bad["layers"][2]["mixer"]["vdim"] = 16          # blending layers must agree on the value shape
     with pytest.raises(ValueError):

@@ -411,6 +411,36 @@ def test_greedy_generation_matches_the_reference(mode):
     eng.runner.close()
 
 
+@pytest.mark.parametrize("mode", ["plain", "graphs"])
+def test_bf16_greedy_generation_on_the_tensor_core_kernels(mode):
+    """Sizes that take the tensor-core attention for prompts and its decode form for generated tokens (also inside a
+    captured graph, with padded rows in the batch bucket). bf16 against the float64 reference: a token may differ only
+    where the reference's two best logits are closer than the arithmetic's noise."""
+    from atx.scheduler import SamplingParams
+
+    cfg = model_cfg([latent_layer(heads=4, dim=32, rot_dim=16, vdim=24, kv_rank=48, q_rank=64, size=70, scale=0.14, mlp=FF),
+                     attention_layer(heads=4, kv=2, dim=64, vdim=32, size=40, scale=0.125, v_mix=True, mlp=FF),
+                     attention_layer(heads=6, kv=2, dim=24, vdim=32, size=90, scale=0.2, v_mix=True)], width=128)
+    wt = R.random_checkpoint(cfg, 17)
+    prompts = [tokens(100, seed=1), tokens(5, seed=2), tokens(64, seed=3)]
+    kw = {"plain": {}, "graphs": {"async_scheduling": True, "enable_cuda_graphs": True}}[mode]
+    eng = engine(cfg, wt, "bfloat16", **kw)
+    outs = eng.generate_sync(prompts, SamplingParams(temperature=0.0, max_tokens=60, ignore_eos=True))
+    close = 0
+    for p, o in zip(prompts, outs):
+        assert len(o) == 60
+        lg = R.forward(cfg, wt, p + o[:-1])[len(p) - 1:]
+        spread = float(lg.std())
+        top2 = lg.topk(2, dim=-1).values
+        for i, tok in enumerate(o):
+            if tok != int(lg[i].argmax()):
+                close += 1
+                assert float(top2[i, 0] - lg[i, tok]) < 0.15 * spread, (mode, i)
+    assert close <= 12
+    assert eng.allocator.num_free == eng.allocator.num_blocks
+    eng.runner.close()
+
+
 def test_generation_over_a_cached_prefix_matches_the_reference():
     """Pages of a shared prefix are attached from the block cache instead of being computed again: they hold blended
     values and latent rows, which depend on the token and its position only, so the continuation must not change."""
