@@ -433,6 +433,10 @@ class Program:
                 if key[1] and key not in self.rot:
                     self.rot[key] = rotation_table(key[0], key[1], e.max_model_len, dev)
         self.first_mix = cfg.first_mix_layer()
+        # second stream for the feed-forward of decode-sized steps (see forward)
+        self.overlap_ffn = True
+        self.side = torch.cuda.Stream(device=dev)
+        self.ev_fork, self.ev_join = torch.cuda.Event(), torch.cuda.Event()
         # scratch of the decode attention's key slices: [tokens, heads, slices, value width + 2] fp32
         self.max_splits = 32
         self.sms = torch.cuda.get_device_properties(dev).multi_processor_count
@@ -508,6 +512,20 @@ class Program:
             nm = l.norm
             ck(lib.atx_tanh_norm(h, None, nm.alpha, nm.w.data_ptr(), nm.b.data_ptr(), xn, T, W, proj if acc else None,
                                  zero_bytes, dt, fl, st))
+            # Decode-sized steps: the feed-forward does not wait for the mixer (both read xn, both ADD into the stream with
+            # red.add), so its two weight-streaming GEMMs run on a second stream beside the mixer's chain of short,
+            # latency-bound kernels; the streams join before the next layer's norm. Inside a captured graph these are two
+            # branches of the layer.
+            side = None
+            if fused_act and T <= 64 and self.overlap_ffn and lin["o"].plan is not None and lin["down"].plan is not None:
+                side = self.side
+                self.ev_fork.record(torch.cuda.current_stream())
+                side.wait_event(self.ev_fork)
+                ss = side.cuda_stream
+                lin["up"].run(self.act_flat.data_ptr(), n_ff, T, fl, ss, mode=_cabi.GEMM_RELU2_BF16)
+                lin["down"].run(h, W, T, fl, ss, mode=ADD)
+                self.ev_join.record(side)
+                n += 2
             lin["in"].run(proj, ld, T, fl, st, zeroed=acc)
             n += 2
             window = int((c.get("mask") or {}).get("size", 0) or 0)
@@ -556,7 +574,9 @@ class Program:
                 n += 5
             lin["o"].run(h, W, T, fl, st, mode=ADD)
             n += 1
-            if "up" in lin:
+            if side is not None:
+                torch.cuda.current_stream().wait_event(self.ev_join)
+            elif "up" in lin:
                 act = self.act_flat.data_ptr()
                 if fused_act:
                     lin["up"].run(act, n_ff, T, fl, st, mode=_cabi.GEMM_RELU2_BF16)

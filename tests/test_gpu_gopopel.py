@@ -418,10 +418,11 @@ def test_bf16_greedy_generation_on_the_tensor_core_kernels(mode):
     where the reference's two best logits are closer than the arithmetic's noise."""
     from atx.scheduler import SamplingParams
 
-    cfg = model_cfg([latent_layer(heads=4, dim=32, rot_dim=16, vdim=24, kv_rank=48, q_rank=64, size=70, scale=0.14, mlp=FF),
-                     attention_layer(heads=4, kv=2, dim=64, vdim=32, size=40, scale=0.125, v_mix=True, mlp=FF),
+    ff = {"ff": 128, "kind": "dense"}      # a multiple of the tcgen05 GEMM's block: decode steps run the feed-forward on
+    cfg = model_cfg([latent_layer(heads=4, dim=32, rot_dim=16, vdim=24, kv_rank=48, q_rank=64, size=70, scale=0.14, mlp=ff),
+                     attention_layer(heads=4, kv=2, dim=64, vdim=32, size=40, scale=0.125, v_mix=True, mlp=ff),
                      attention_layer(heads=6, kv=2, dim=24, vdim=32, size=90, scale=0.2, v_mix=True)], width=128)
-    wt = R.random_checkpoint(cfg, 17)
+    wt = R.random_checkpoint(cfg, 17)      # a second stream beside the mixer (two branches of a captured graph)
     prompts = [tokens(100, seed=1), tokens(5, seed=2), tokens(64, seed=3)]
     kw = {"plain": {}, "graphs": {"async_scheduling": True, "enable_cuda_graphs": True}}[mode]
     eng = engine(cfg, wt, "bfloat16", **kw)
