@@ -235,6 +235,9 @@ def test_deterministic_mode_repeats_itself_bit_for_bit():
         rows = []
         while eng.has_work():
             if eng.step():
+                # a chained step may already be in flight on the runner's stream: wait for it, so that the snapshot does
+                # not depend on how far it has got (the launch order itself is the scheduler's and repeats exactly)
+                eng.runner.stream.synchronize()
                 rows.append(eng.runner.logits[:6].clone())
         outs.append(([s.output_ids for s in seqs], torch.stack(rows).cpu()))
     assert outs[0][0] == outs[1][0]
