@@ -285,7 +285,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_con
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;             // row inside the tile == TMEM lane
         const int qpos = m0 + t * kTcBM + row;           // query index inside this sequence's chunk
-        const int limit = off + qpos;                    // last visible key
+        // last visible key. Rows past the chunk (the tile is padded to 128 rows) are capped at the context too: beyond it
+        // the key tile holds stale page contents or shared memory that was never loaded, and although such a row's output
+        // is dropped, its scores take part in the warp-wide vote below that moves the exponent reference of its
+        // neighbours, whose rounding would then depend on what ran on the SM before.
+        const int limit = min(off + qpos, ctx - 1);
         const int first_limit = off + m0 + t * kTcBM;    // ... of the tile's first row (CTA-uniform per tile)
         const uint32_t lane_sel = static_cast<uint32_t>(quarter * 32) << 16;
         const uint32_t tmem_S = tmem_base + t * 128 + lane_sel;
